@@ -1,0 +1,59 @@
+// Shared device/host helpers for the sm_100a kernels in this directory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../../include/cuda_agent_b200.h"
+
+namespace cab {
+
+constexpr int kWarp = 32;
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+__host__ __device__ inline bool aligned_to(const void* p, size_t bytes) {
+  return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0;
+}
+
+// Status a launcher returns after enqueueing: catches bad launch configurations
+// without synchronising the stream.
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? CAB_OK : CAB_ERR_LAUNCH; }
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+  return x;
+}
+
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, off));
+  return x;
+}
+
+// bf16 bits -> fp32 is a 16-bit shift; exact.
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) {
+  return __uint_as_float(packed & 0xffff0000u);
+}
+
+// Streaming 128-bit global accesses: data touched once, so it is marked
+// evict-first in L1 and L2 instead of displacing anything reusable.
+// The load is `asm volatile` so that it is issued exactly once, where it is
+// written: a kernel that posts N loads before the first use keeps N in flight.
+__device__ __forceinline__ float4 ld_stream(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.cs.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(float4* p, float4 v) {
+  asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};"
+               :
+               : "l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+}  // namespace cab
