@@ -48,8 +48,8 @@ H2D_BYTES = 2 * B * HQ * D * 2 + B * HV * D * 2 + 2 * B * HV * 4
 D2H_BYTES = B * HV * D * 4
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one gdn_decode_kernel launch at this
-# workload, from the ncu capture summarised in profiles/; None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# workload, from the ncu capture summarised in profiles/gdn_decode_kernel_config1.md.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1024897792
 
 
 def parse_args():
