@@ -1,0 +1,288 @@
+// MoE token movement for sm_100a: the stable expert permutation, the fused
+// 1x128 e4m3 quantise-and-dispatch of activations, and the weighted combine.
+//
+// Row space of the grouped GEMMs. The flat list of (token, slot) entries
+// i = t*k + slot is stably sorted by expert id; entry i lands at sorted position
+// inv_perm[i] (perm is the inverse). Each expert's run of rows is then placed at
+// a 128-aligned start in a padded row space, so that every 128-row GEMM tile
+// belongs to exactly one expert:
+//     dst_row[i] = pad_offsets[e] + (inv_perm[i] - offsets[e])
+// tile_expert[j] names the expert of padded tile j, num_tiles[0] counts the used
+// tiles. Padding rows are never written and never read back.
+//
+// The permutation is scan based (no atomics decide a position), so it is the
+// same on every run and equal to a CPU stable sort.
+#include "cab_common.cuh"
+
+#include <cuda_fp8.h>
+
+namespace {
+
+constexpr int kChunk = 1024;     // entries per CTA in the count / rank kernels
+constexpr int kMaxE = 256;
+constexpr int kTileM = 128;
+
+// Per-warp, per-expert population of this CTA's chunk, in shared memory:
+// wc[w][e] = number of entries of expert e among warp w's 32 consecutive entries.
+__device__ __forceinline__ void chunk_warp_counts(int (*wc)[kMaxE], const int* __restrict__ idx,
+                                                  int n, int E, int& my_e, int& rank_in_warp,
+                                                  bool& out_of_range) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) wc[i / E][i % E] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kChunk + threadIdx.x;
+  my_e = i < n ? __ldg(idx + i) : -1;
+  out_of_range = i < n && (my_e < 0 || my_e >= E);
+  if (out_of_range) my_e = -1;   // flagged by the caller, otherwise ignored
+  // lanes past the end all carry -1 and only match each other
+  const unsigned peers = __match_any_sync(0xffffffffu, my_e);
+  rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (my_e >= 0 && rank_in_warp == 0) wc[warp][my_e] = __popc(peers);
+  __syncthreads();
+}
+
+// Kernel 1: per-chunk expert counts; the last CTA to finish turns them into
+// chunk bases, expert offsets, padded offsets and the tile table.
+__global__ void __launch_bounds__(kChunk)
+moe_count_scan_kernel(const int* __restrict__ idx, int n, int E, int nchunks,
+                      int* __restrict__ chunk_cnt,   // [nchunks][E], becomes exclusive chunk bases
+                      unsigned* __restrict__ done_counter,
+                      int* __restrict__ counts, int* __restrict__ offsets,
+                      int* __restrict__ pad_offsets, int* __restrict__ tile_expert,
+                      int* __restrict__ num_tiles, int max_tiles, int* __restrict__ status) {
+  __shared__ int wc[32][kMaxE];
+  __shared__ bool is_last;
+  int my_e, rank;
+  bool bad;
+  chunk_warp_counts(wc, idx, n, E, my_e, rank, bad);
+  if (bad && status) atomicExch(status, 1);   // expert id out of range: flagged, entry ignored
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int c = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) c += wc[w][e];
+    chunk_cnt[(size_t)blockIdx.x * E + e] = c;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(done_counter, 1u) == (unsigned)nchunks - 1u);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // exclusive scan over chunks, one thread per expert
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < nchunks; ++c) {
+      const int v = __ldcg(chunk_cnt + (size_t)c * E + e);
+      chunk_cnt[(size_t)c * E + e] = run;
+      run += v;
+    }
+    counts[e] = run;
+    wc[0][e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, pad = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = wc[0][e];
+      offsets[e] = off;
+      pad_offsets[e] = pad;
+      const int nt = (c + kTileM - 1) / kTileM;
+      for (int j = 0; j < nt && tiles + j < max_tiles; ++j) tile_expert[tiles + j] = e;
+      off += c;
+      pad += nt * kTileM;
+      tiles += nt;
+    }
+    offsets[E] = off;
+    pad_offsets[E] = pad;
+    if (tiles > max_tiles && status) atomicExch(status, 2);
+    num_tiles[0] = min(tiles, max_tiles);
+    for (int j = min(tiles, max_tiles); j < max_tiles; ++j) tile_expert[j] = -1;
+    *done_counter = 0;   // ready for the next call
+  }
+}
+
+// Kernel 2: position of every entry.
+__global__ void __launch_bounds__(kChunk)
+moe_rank_kernel(const int* __restrict__ idx, int n, int E, const int* __restrict__ chunk_base,
+                const int* __restrict__ offsets, const int* __restrict__ pad_offsets,
+                int* __restrict__ perm, int* __restrict__ inv_perm, int* __restrict__ dst_row) {
+  __shared__ int wc[32][kMaxE];
+  int my_e, rank;
+  bool bad;
+  chunk_warp_counts(wc, idx, n, E, my_e, rank, bad);
+  // exclusive scan over the 32 warps, one thread per expert
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) { const int v = wc[w][e]; wc[w][e] = run; run += v; }
+  }
+  __syncthreads();
+  const int i = blockIdx.x * kChunk + threadIdx.x;
+  if (i < n && my_e >= 0) {
+    const int within = __ldg(chunk_base + (size_t)blockIdx.x * E + my_e) + wc[threadIdx.x >> 5][my_e] + rank;
+    const int pos = __ldg(offsets + my_e) + within;
+    inv_perm[i] = pos;
+    perm[pos] = i;
+    dst_row[i] = __ldg(pad_offsets + my_e) + within;
+  }
+}
+
+// ------------------------------------------------------------------ quantise + dispatch
+// amax floor and the e4m3 maximum of the 1x128 quantisation rule.
+constexpr float kAmaxFloor = 1e-4f;
+constexpr float kFp8Max = 448.f;
+
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+// One warp per token. Per pass the warp covers 256 columns: a lane reads 8 bf16
+// (16 bytes); a 128-column quantisation block is a half-warp. The quantised row
+// is written to every destination row of the token (k of them, or row t itself
+// when dst_row is null), scales go to the transposed table sc_t[block][row].
+__global__ void __launch_bounds__(256)
+moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int k,
+                          const int* __restrict__ dst_row, uint8_t* __restrict__ a_q,
+                          float* __restrict__ sc_t, int ld_rows) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  int my_dst = t;
+  if (dst_row) my_dst = lane < k ? __ldg(dst_row + (size_t)t * k + lane) : -1;
+  const int ndst = dst_row ? k : 1;
+  const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+  for (int c0 = 0; c0 < H; c0 += 256) {
+    const int col = c0 + lane * 8;
+    const bool live = col < H;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = __ldg(xrow + (col >> 3));
+    float v[8] = {cab::bf16_lo(raw.x), cab::bf16_hi(raw.x), cab::bf16_lo(raw.y), cab::bf16_hi(raw.y),
+                  cab::bf16_lo(raw.z), cab::bf16_hi(raw.z), cab::bf16_lo(raw.w), cab::bf16_hi(raw.w)};
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float scale = __fdiv_rn(fmaxf(amax, kAmaxFloor), kFp8Max);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __fdiv_rn(v[j], scale);
+    const uint2 q = make_uint2(pack4_e4m3(v[0], v[1], v[2], v[3]), pack4_e4m3(v[4], v[5], v[6], v[7]));
+    for (int s = 0; s < ndst; ++s) {
+      const int row = dst_row ? __shfl_sync(0xffffffffu, my_dst, s) : t;
+      if (live && row >= 0) {
+        *reinterpret_cast<uint2*>(a_q + (size_t)row * H + col) = q;
+        if ((lane & 15) == 0) sc_t[(size_t)(col >> 7) * ld_rows + row] = scale;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ combine
+// out[t] = sum over slots (ascending) of w[t,slot] * y[dst_row[t*k+slot]] (+ extra[t]),
+// fp32 accumulate, bf16 result. One CTA per token, 16-byte accesses.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ y,
+                   const int* __restrict__ dst_row, const float* __restrict__ w,
+                   const __nv_bfloat16* __restrict__ extra, int T, int H, int k) {
+  const int t = blockIdx.x;
+  __shared__ int rows[32];
+  __shared__ float wts[32];
+  if (threadIdx.x < k) {
+    rows[threadIdx.x] = __ldg(dst_row + (size_t)t * k + threadIdx.x);
+    wts[threadIdx.x] = __ldg(w + (size_t)t * k + threadIdx.x);
+  }
+  __syncthreads();
+  for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < k; ++s) {
+      const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[s] * H + col));
+      const float ws = wts[s];
+      acc[0] = fmaf(ws, cab::bf16_lo(raw.x), acc[0]); acc[1] = fmaf(ws, cab::bf16_hi(raw.x), acc[1]);
+      acc[2] = fmaf(ws, cab::bf16_lo(raw.y), acc[2]); acc[3] = fmaf(ws, cab::bf16_hi(raw.y), acc[3]);
+      acc[4] = fmaf(ws, cab::bf16_lo(raw.z), acc[4]); acc[5] = fmaf(ws, cab::bf16_hi(raw.z), acc[5]);
+      acc[6] = fmaf(ws, cab::bf16_lo(raw.w), acc[6]); acc[7] = fmaf(ws, cab::bf16_hi(raw.w), acc[7]);
+    }
+    if (extra) {
+      const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(extra + (size_t)t * H + col));
+      acc[0] += cab::bf16_lo(raw.x); acc[1] += cab::bf16_hi(raw.x);
+      acc[2] += cab::bf16_lo(raw.y); acc[3] += cab::bf16_hi(raw.y);
+      acc[4] += cab::bf16_lo(raw.z); acc[5] += cab::bf16_hi(raw.z);
+      acc[6] += cab::bf16_lo(raw.w); acc[7] += cab::bf16_hi(raw.w);
+    }
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]), p1 = __floats2bfloat162_rn(acc[2], acc[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]), p3 = __floats2bfloat162_rn(acc[6], acc[7]);
+    uint4 o;
+    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+    *reinterpret_cast<uint4*>(out + (size_t)t * H + col) = o;
+  }
+}
+
+}  // namespace
+
+extern "C" size_t moe_permute_scratch_bytes(int T, int k, int E) {
+  const long long n = (long long)T * k;
+  const long long nchunks = (n + kChunk - 1) / kChunk;
+  return (size_t)(nchunks * E + 2) * sizeof(int);
+}
+
+extern "C" int moe_permute_max_tiles(int T, int k, int E) {
+  // every expert can waste at most one partial tile
+  const long long n = (long long)T * k;
+  return (int)(n / kTileM + E);
+}
+
+extern "C" int moe_permute_launcher(const int* topk_idx, int T, int k, int E, int* counts,
+                                    int* offsets, int* pad_offsets, int* perm, int* inv_perm,
+                                    int* dst_row, int* tile_expert, int* num_tiles, int max_tiles,
+                                    void* scratch, int config, cudaStream_t stream) {
+  (void)config;
+  if (!counts || !offsets || !pad_offsets || !tile_expert || !num_tiles || !scratch)
+    return CAB_ERR_BAD_ARGUMENT;
+  if (T < 0 || k <= 0 || E <= 0 || E > kMaxE || max_tiles <= 0) return CAB_ERR_BAD_ARGUMENT;
+  const long long n = (long long)T * k;
+  if (n > 0 && (!topk_idx || !perm || !inv_perm || !dst_row)) return CAB_ERR_BAD_ARGUMENT;
+  if (n > (1LL << 30)) return CAB_ERR_TOO_LARGE;
+  const int nchunks = n == 0 ? 1 : (int)((n + kChunk - 1) / kChunk);
+  int* chunk_cnt = static_cast<int*>(scratch);
+  unsigned* done = reinterpret_cast<unsigned*>(chunk_cnt + (size_t)nchunks * E);
+  int* status = chunk_cnt + (size_t)nchunks * E + 1;
+  if (cudaMemsetAsync(done, 0, 2 * sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
+  moe_count_scan_kernel<<<nchunks, kChunk, 0, stream>>>(topk_idx, (int)n, E, nchunks, chunk_cnt, done,
+                                                        counts, offsets, pad_offsets, tile_expert,
+                                                        num_tiles, max_tiles, status);
+  if (n > 0)
+    moe_rank_kernel<<<nchunks, kChunk, 0, stream>>>(topk_idx, (int)n, E, chunk_cnt, offsets,
+                                                    pad_offsets, perm, inv_perm, dst_row);
+  return cab::launch_status();
+}
+
+extern "C" int moe_quant_dispatch_launcher(cab_e4m3* a_q, float* scales_t, const cab_bf16* x,
+                                           const int* dst_row, int T, int H, int k, int ld_rows,
+                                           int config, cudaStream_t stream) {
+  (void)config;
+  if (T == 0) return CAB_OK;
+  if (!a_q || !scales_t || !x) return CAB_ERR_BAD_ARGUMENT;
+  if (T < 0 || H <= 0 || H % 128 != 0 || k <= 0 || k > 32 || ld_rows <= 0) return CAB_ERR_BAD_ARGUMENT;
+  if (!cab::aligned_to(a_q, 16) || !cab::aligned_to(x, 16)) return CAB_ERR_MISALIGNED;
+  moe_quant_dispatch_kernel<<<(T + 7) / 8, 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), T, H, k, dst_row, a_q, scales_t, ld_rows);
+  return cab::launch_status();
+}
+
+extern "C" int moe_combine_launcher(cab_bf16* out, const cab_bf16* y, const int* dst_row,
+                                    const float* weights, const cab_bf16* extra, int T, int H, int k,
+                                    int config, cudaStream_t stream) {
+  (void)config;
+  if (T == 0) return CAB_OK;
+  if (!out || !y || !dst_row || !weights) return CAB_ERR_BAD_ARGUMENT;
+  if (T < 0 || H <= 0 || H % 8 != 0 || k <= 0 || k > 32) return CAB_ERR_BAD_ARGUMENT;
+  if (!cab::aligned_to(out, 16) || !cab::aligned_to(y, 16) || (extra && !cab::aligned_to(extra, 16)))
+    return CAB_ERR_MISALIGNED;
+  moe_combine_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(out),
+                                            reinterpret_cast<const __nv_bfloat16*>(y), dst_row, weights,
+                                            reinterpret_cast<const __nv_bfloat16*>(extra), T, H, k);
+  return cab::launch_status();
+}

@@ -1,0 +1,262 @@
+// MoE routing for sm_100a: router logits and the two top-k rules.
+//
+//   moe_router_logits   logits[t, e] = sum_h x[t, h] * wr[e, h]   bf16 in, fp32 out
+//   moe_route_softmax   k largest logits per token (descending, ties -> lower
+//                       expert id) and the softmax over just those k
+//   moe_route_sigmoid   DeepSeek-V3 style: s = sigmoid(logit), c = s + bias, keep the
+//                       best `topk_group` of `n_group` expert groups (group score =
+//                       sum of its two largest c), then the k largest c inside them;
+//                       weights s[idx] / sum(s[idx]) * scale
+//
+// Index outputs are meant to be bit-identical to a CPU statement of the same
+// rules, so every comparison that decides an index uses only values that are
+// reproducible bit for bit: raw fp32 logits for the softmax rule, and for the
+// sigmoid rule a sigmoid evaluated in fp64 and rounded once to fp32 followed by
+// IEEE fp32 adds (no fast-math approximations on that path).
+//
+// The selection kernels run one warp per token with the token's E <= 256 scores
+// spread over the lanes (expert e lives in lane e % 32, slot e / 32).
+#include "cab_common.cuh"
+
+namespace {
+
+constexpr int kMaxE = 256;
+constexpr int kSlots = kMaxE / 32;
+constexpr int kMaxTopK = 32;
+
+// ------------------------------------------------------------------ logits
+// One warp computes 16 tokens x (up to) 64 experts per pass with mma.sync
+// m16n8k16 bf16 (fp32 accumulate). Fragments come straight from global memory:
+// a lane reads 16 contiguous bytes (8 bf16) of its A rows and of its B row and
+// feeds them to two MMAs. That assigns the k index inside a 32-wide chunk in a
+// permuted order, identically for A and B, which a dot product does not notice.
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1,
+                                                 uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+router_logits_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
+                     const __nv_bfloat16* __restrict__ wr, int T, int H, int E) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int t0 = warp_global * 16;
+  if (t0 >= T) return;
+  const int r = lane >> 2;          // fragment row within 8
+  const int kq = (lane & 3) * 8;    // this lane's 8 consecutive k inside a 32-chunk
+  const int ta = min(t0 + r, T - 1), tb = min(t0 + r + 8, T - 1);
+  const uint4* xa = reinterpret_cast<const uint4*>(x + (size_t)ta * H + kq);
+  const uint4* xb = reinterpret_cast<const uint4*>(x + (size_t)tb * H + kq);
+
+  for (int e0 = 0; e0 < E; e0 += 64) {
+    const int ntiles = min(8, (E - e0) >> 3);
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const __nv_bfloat16* wbase = wr + (size_t)(e0 + r) * H + kq;
+    for (int k0 = 0; k0 < H; k0 += 32) {
+      const uint4 a_lo = __ldg(xa + (k0 >> 3));
+      const uint4 a_hi = __ldg(xb + (k0 >> 3));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j < ntiles) {
+          const uint4 b = __ldg(reinterpret_cast<const uint4*>(wbase + (size_t)j * 8 * H + k0));
+          mma_bf16_16x8x16(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+          mma_bf16_16x8x16(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+        }
+      }
+    }
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < ntiles) {
+        const int e = e0 + j * 8 + col;
+        if (t0 + r < T)
+          *reinterpret_cast<float2*>(logits + (size_t)(t0 + r) * E + e) = make_float2(acc[j][0], acc[j][1]);
+        if (t0 + r + 8 < T)
+          *reinterpret_cast<float2*>(logits + (size_t)(t0 + r + 8) * E + e) = make_float2(acc[j][2], acc[j][3]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ selection
+// (value, index) ordering used everywhere: larger value first, equal values ->
+// smaller index first.
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+  return v > bv || (v == bv && i < bi);
+}
+
+// Picks the best remaining entry of the warp-distributed array `val` (slot j of
+// lane l is entry j*32+l; entries whose bit is set in `taken` are skipped, as are
+// entries >= n). Every lane returns the same (value, index); index -1 if none is left.
+__device__ __forceinline__ void warp_argbest(const float (&val)[kSlots], uint32_t taken, int n,
+                                             int lane, float& best_v, int& best_i) {
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+#pragma unroll
+  for (int j = 0; j < kSlots; ++j) {
+    const int e = j * 32 + lane;
+    if (e < n && !((taken >> j) & 1u) && better(val[j], e, bv, bi)) { bv = val[j]; bi = e; }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  best_v = bv;
+  best_i = (bi == 0x7fffffff) ? -1 : bi;
+}
+
+__global__ void __launch_bounds__(256)
+route_softmax_topk_kernel(int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                          const float* __restrict__ logits, int T, int E, int k) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  float val[kSlots];
+#pragma unroll
+  for (int j = 0; j < kSlots; ++j) {
+    const int e = j * 32 + lane;
+    val[j] = e < E ? __ldg(logits + (size_t)t * E + e) : -INFINITY;
+  }
+  uint32_t taken = 0;
+  float my_v = 0.f, top_v = 0.f, denom = 0.f;
+  int my_i = 0;
+  for (int s = 0; s < k; ++s) {
+    float bv; int bi;
+    warp_argbest(val, taken, E, lane, bv, bi);
+    if (bi >= 0 && (bi & 31) == lane) taken |= 1u << (bi >> 5);
+    if (s == 0) top_v = bv;
+    const float p = expf(bv - top_v);
+    denom += p;
+    if (lane == s) { my_v = p; my_i = bi; }
+  }
+  if (lane < k) {
+    topk_idx[(size_t)t * k + lane] = my_i;
+    topk_w[(size_t)t * k + lane] = __fdividef(my_v, denom);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+route_sigmoid_group_topk_kernel(int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                const float* __restrict__ logits, const float* __restrict__ bias,
+                                int T, int E, int k, int n_group, int topk_group, float scale) {
+  __shared__ float c_sm[8][kMaxE];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float s_val[kSlots], c_val[kSlots];
+#pragma unroll
+  for (int j = 0; j < kSlots; ++j) {
+    const int e = j * 32 + lane;
+    if (e < E) {
+      const double l = (double)__ldg(logits + (size_t)t * E + e);
+      s_val[j] = (float)(1.0 / (1.0 + exp(-l)));          // fp64 sigmoid, rounded once
+      c_val[j] = __fadd_rn(s_val[j], __ldg(bias + e));
+      c_sm[warp][e] = c_val[j];
+    } else {
+      s_val[j] = 0.f;
+      c_val[j] = -INFINITY;
+    }
+  }
+  __syncwarp();
+  // group scores: lane g scans group g (n_group <= 32)
+  const int gsize = E / n_group;
+  float gscore[kSlots];
+#pragma unroll
+  for (int j = 0; j < kSlots; ++j) gscore[j] = -INFINITY;
+  if (lane < n_group) {
+    float m1 = -INFINITY, m2 = -INFINITY;
+    for (int i = 0; i < gsize; ++i) {
+      const float v = c_sm[warp][lane * gsize + i];
+      if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
+    }
+    gscore[0] = gsize >= 2 ? __fadd_rn(m1, m2) : m1;
+  }
+  uint32_t g_taken = 0, keep_mask = 0;
+  for (int s = 0; s < topk_group; ++s) {
+    float bv; int bi;
+    warp_argbest(gscore, g_taken, n_group, lane, bv, bi);
+    if (bi >= 0) {
+      keep_mask |= 1u << bi;
+      if (bi == lane) g_taken |= 1u;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kSlots; ++j) {
+    const int e = j * 32 + lane;
+    if (e < E && !((keep_mask >> (e / gsize)) & 1u)) c_val[j] = -INFINITY;
+  }
+  uint32_t taken = 0;
+  float my_s = 0.f, denom = 0.f;
+  int my_i = 0;
+  for (int s = 0; s < k; ++s) {
+    float bv; int bi;
+    warp_argbest(c_val, taken, E, lane, bv, bi);
+    float sv = 0.f;
+    if (bi >= 0 && (bi & 31) == lane) {
+      taken |= 1u << (bi >> 5);
+#pragma unroll
+      for (int j = 0; j < kSlots; ++j) if (j == (bi >> 5)) sv = s_val[j];
+    }
+    sv = __shfl_sync(0xffffffffu, sv, bi >= 0 ? (bi & 31) : 0);
+    denom += sv;
+    if (lane == s) { my_s = sv; my_i = bi; }
+  }
+  if (lane < k) {
+    topk_idx[(size_t)t * k + lane] = my_i;
+    topk_w[(size_t)t * k + lane] = __fdiv_rn(my_s, denom) * scale;
+  }
+}
+
+bool route_args_ok(int T, int E, int k) { return T >= 0 && E > 0 && E <= kMaxE && k > 0 && k <= kMaxTopK && k <= E; }
+
+}  // namespace
+
+extern "C" int moe_router_logits_launcher(float* logits, const cab_bf16* x, const cab_bf16* wr,
+                                          int T, int H, int E, int config, cudaStream_t stream) {
+  (void)config;
+  if (T == 0) return CAB_OK;
+  if (!logits || !x || !wr) return CAB_ERR_BAD_ARGUMENT;
+  if (T < 0 || H <= 0 || E <= 0 || H % 32 != 0 || E % 8 != 0) return CAB_ERR_BAD_ARGUMENT;
+  if (!cab::aligned_to(x, 16) || !cab::aligned_to(wr, 16) || !cab::aligned_to(logits, 8))
+    return CAB_ERR_MISALIGNED;
+  const int warps = (T + 15) / 16;
+  router_logits_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(
+      logits, reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(wr),
+      T, H, E);
+  return cab::launch_status();
+}
+
+extern "C" int moe_route_softmax_topk_launcher(int* topk_idx, float* topk_w, const float* logits,
+                                               int T, int E, int k, int config, cudaStream_t stream) {
+  (void)config;
+  if (T == 0) return CAB_OK;
+  if (!topk_idx || !topk_w || !logits || !route_args_ok(T, E, k)) return CAB_ERR_BAD_ARGUMENT;
+  route_softmax_topk_kernel<<<(T + 7) / 8, 256, 0, stream>>>(topk_idx, topk_w, logits, T, E, k);
+  return cab::launch_status();
+}
+
+extern "C" int moe_route_sigmoid_group_topk_launcher(int* topk_idx, float* topk_w,
+                                                     const float* logits, const float* bias, int T,
+                                                     int E, int k, int n_group, int topk_group,
+                                                     float routed_scaling_factor, int config,
+                                                     cudaStream_t stream) {
+  (void)config;
+  if (T == 0) return CAB_OK;
+  if (!topk_idx || !topk_w || !logits || !bias || !route_args_ok(T, E, k)) return CAB_ERR_BAD_ARGUMENT;
+  if (n_group <= 0 || n_group > 32 || E % n_group != 0 || topk_group <= 0 || topk_group > n_group ||
+      k > topk_group * (E / n_group))
+    return CAB_ERR_BAD_ARGUMENT;
+  route_sigmoid_group_topk_kernel<<<(T + 7) / 8, 256, 0, stream>>>(
+      topk_idx, topk_w, logits, bias, T, E, k, n_group, topk_group, routed_scaling_factor);
+  return cab::launch_status();
+}

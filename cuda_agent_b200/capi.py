@@ -8,7 +8,7 @@ reach the kernels without going through pybind.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libcuda_agent_b200.so"
@@ -19,6 +19,14 @@ SIGNATURES = {
     "cab_version": (c_int, []),
     "axpby_launcher": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p]),
     "gdn_decode_launcher": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "moe_router_logits_launcher": (c_int, [c_void_p] * 3 + [c_int] * 4 + [c_void_p]),
+    "moe_route_softmax_topk_launcher": (c_int, [c_void_p] * 3 + [c_int] * 4 + [c_void_p]),
+    "moe_route_sigmoid_group_topk_launcher": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_float, c_int, c_void_p]),
+    "moe_permute_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "moe_permute_max_tiles": (c_int, [c_int, c_int, c_int]),
+    "moe_permute_launcher": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p]),
+    "moe_quant_dispatch_launcher": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
+    "moe_combine_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),
 }
 
 
@@ -79,3 +87,66 @@ def gdn_decode(state, out, q, k, v, g, beta, config: int = 0) -> None:
     _check("gdn_decode_launcher",
            lib().gdn_decode_launcher(_p(state), _p(out), _p(q), _p(k), _p(v), _p(g), _p(beta),
                                      B, Hq, Hv, config, _stream()))
+
+
+# ----------------------------------------------------------------------------- MoE stages
+def _opt(t):
+    return None if t is None else _p(t)
+
+
+def moe_router_logits(logits, x, wr, config: int = 0) -> None:
+    T, H = x.shape
+    _check("moe_router_logits_launcher",
+           lib().moe_router_logits_launcher(_p(logits), _p(x), _p(wr), T, H, wr.shape[0], config, _stream()))
+
+
+def moe_route_softmax_topk(topk_idx, topk_w, logits, config: int = 0) -> None:
+    T, E = logits.shape
+    _check("moe_route_softmax_topk_launcher",
+           lib().moe_route_softmax_topk_launcher(_p(topk_idx), _p(topk_w), _p(logits), T, E,
+                                                 topk_idx.shape[1], config, _stream()))
+
+
+def moe_route_sigmoid_group_topk(topk_idx, topk_w, logits, bias, n_group, topk_group, scale=1.0,
+                                 config: int = 0) -> None:
+    T, E = logits.shape
+    _check("moe_route_sigmoid_group_topk_launcher",
+           lib().moe_route_sigmoid_group_topk_launcher(_p(topk_idx), _p(topk_w), _p(logits), _p(bias), T, E,
+                                                       topk_idx.shape[1], n_group, topk_group, scale,
+                                                       config, _stream()))
+
+
+def moe_permute(topk_idx, E: int):
+    """Allocates and returns the permutation tables for topk_idx [T, k] (int32, CUDA)."""
+    import torch
+    T, k = topk_idx.shape
+    dev = topk_idx.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    max_tiles = lib().moe_permute_max_tiles(T, k, E)
+    out = dict(counts=torch.empty(E, **i32), offsets=torch.empty(E + 1, **i32),
+               pad_offsets=torch.empty(E + 1, **i32), perm=torch.empty(T * k, **i32),
+               inv_perm=torch.empty(T * k, **i32), dst_row=torch.empty(T * k, **i32),
+               tile_expert=torch.empty(max_tiles, **i32), num_tiles=torch.empty(1, **i32),
+               max_tiles=max_tiles)
+    scratch = torch.empty(lib().moe_permute_scratch_bytes(T, k, E), dtype=torch.uint8, device=dev)
+    _check("moe_permute_launcher",
+           lib().moe_permute_launcher(_p(topk_idx), T, k, E, _p(out["counts"]), _p(out["offsets"]),
+                                      _p(out["pad_offsets"]), _p(out["perm"]), _p(out["inv_perm"]),
+                                      _p(out["dst_row"]), _p(out["tile_expert"]), _p(out["num_tiles"]),
+                                      max_tiles, _p(scratch), 0, _stream()))
+    out["scratch"] = scratch
+    return out
+
+
+def moe_quant_dispatch(a_q, scales_t, x, dst_row, k: int, config: int = 0) -> None:
+    T, H = x.shape
+    _check("moe_quant_dispatch_launcher",
+           lib().moe_quant_dispatch_launcher(_p(a_q), _p(scales_t), _p(x), _opt(dst_row), T, H, k,
+                                             scales_t.shape[1], config, _stream()))
+
+
+def moe_combine(out, y, dst_row, weights, extra=None, config: int = 0) -> None:
+    T, H = out.shape
+    _check("moe_combine_launcher",
+           lib().moe_combine_launcher(_p(out), _p(y), _p(dst_row), _p(weights), _opt(extra), T, H,
+                                      weights.shape[1], config, _stream()))

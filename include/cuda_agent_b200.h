@@ -84,6 +84,78 @@ int gdn_decode_launcher(float* state, float* out, const cab_bf16* q, const cab_b
                         const cab_bf16* v, const float* g, const float* beta, int B, int Hq,
                         int Hv, int config, cab_stream_t stream);
 
+/* ------------------------------------------------------------------------- */
+/* FP8 block-scaled MoE layer. The reference ships no such op; each launcher   */
+/* below fills the slot agent_workdir/kernels/<op>.cu gives a kernel (launcher */
+/* ABI of agent_workdir/kernels/axpby.cu:12-20), one per stage of               */
+/*   logits -> top-k routing -> stable expert permutation -> 1x128 e4m3         */
+/*   quantise + dispatch -> grouped FP8 GEMM (gate/up, SwiGLU, re-quantise) ->  */
+/*   grouped FP8 GEMM (down) -> weighted combine.                               */
+/* Shapes: T tokens, hidden H, expert intermediate I, E experts (<= 256),      */
+/* k experts per token (<= 32).                                                */
+/* ------------------------------------------------------------------------- */
+
+/* logits[T,E] (fp32) = x[T,H] (bf16) . wr[E,H]^T (bf16), fp32 accumulation.   */
+/* H % 32 == 0, E % 8 == 0; x and wr 16-byte aligned.                           */
+int moe_router_logits_launcher(float* logits, const cab_bf16* x, const cab_bf16* wr, int T, int H,
+                               int E, int config, cab_stream_t stream);
+
+/* Softmax routing: topk_idx[T,k] (int32) = the k largest logits per token in   */
+/* descending order, equal logits -> lower expert id first; topk_w[T,k] (fp32)  */
+/* = softmax over those k logits (the full softmax renormalised to sum 1).      */
+int moe_route_softmax_topk_launcher(int* topk_idx, float* topk_w, const float* logits, int T, int E,
+                                    int k, int config, cab_stream_t stream);
+
+/* Sigmoid routing with a bias and group restriction: s = sigmoid(logit)        */
+/* (evaluated in fp64, rounded to fp32), c = s + bias[e]; experts form n_group   */
+/* contiguous groups; a group scores the sum of its two largest c; the          */
+/* topk_group best groups are kept (ties -> lower group); topk_idx = the k       */
+/* largest c among kept groups (descending, ties -> lower id);                   */
+/* topk_w = s[idx] / sum(s[idx]) * routed_scaling_factor. n_group <= 32.         */
+int moe_route_sigmoid_group_topk_launcher(int* topk_idx, float* topk_w, const float* logits,
+                                          const float* bias, int T, int E, int k, int n_group,
+                                          int topk_group, float routed_scaling_factor, int config,
+                                          cab_stream_t stream);
+
+/* Bytes of scratch moe_permute_launcher needs, and the number of 128-row tiles  */
+/* the padded row space can hold (T*k/128 + E). Host-only helpers.               */
+size_t moe_permute_scratch_bytes(int T, int k, int E);
+int moe_permute_max_tiles(int T, int k, int E);
+
+/* Stable sort of the T*k flat entries i = t*k + slot by expert id.              */
+/*   counts[E], offsets[E+1]      per-expert population and its exclusive scan   */
+/*   pad_offsets[E+1]             the same with every expert rounded up to 128    */
+/*   perm[T*k], inv_perm[T*k]     perm[p] = entry at sorted position p; inverse   */
+/*   dst_row[T*k]                 row of entry i in the padded (128-aligned per   */
+/*                                expert) row space the grouped GEMMs work in     */
+/*   tile_expert[max_tiles]       expert of each 128-row tile (-1 when unused)    */
+/*   num_tiles[1]                 tiles in use                                    */
+/* scratch: moe_permute_scratch_bytes() bytes of device memory, contents         */
+/* irrelevant on entry. Positions come from scans, never from atomics, so the     */
+/* result equals a CPU stable sort on every run. Out-of-range expert ids are      */
+/* skipped and flagged in the last int of scratch (1), as is tile overflow (2).   */
+int moe_permute_launcher(const int* topk_idx, int T, int k, int E, int* counts, int* offsets,
+                         int* pad_offsets, int* perm, int* inv_perm, int* dst_row, int* tile_expert,
+                         int* num_tiles, int max_tiles, void* scratch, int config,
+                         cab_stream_t stream);
+
+/* 1x128 e4m3 quantisation of x[T,H] (bf16) fused with the dispatch copy.        */
+/* Per token and 128-column block: amax = max|x| floored at 1e-4, scale =         */
+/* amax/448, q = e4m3(x/scale) (round to nearest even, saturating; both           */
+/* divisions IEEE fp32). The quantised row goes to rows dst_row[t*k+slot] of      */
+/* a_q[*,H] for slot < k (dst_row == NULL: k is ignored and row t is written),    */
+/* its scales to scales_t[block * ld_rows + row] (block-major, "transposed").     */
+int moe_quant_dispatch_launcher(cab_e4m3* a_q, float* scales_t, const cab_bf16* x,
+                                const int* dst_row, int T, int H, int k, int ld_rows, int config,
+                                cab_stream_t stream);
+
+/* out[t,:] (bf16) = sum over slot = 0..k-1, in that order, of                   */
+/* weights[t,slot] * y[dst_row[t*k+slot], :] (+ extra[t,:] when non-NULL), fp32   */
+/* accumulation. y, extra, out are bf16 with row length H (H % 8 == 0).           */
+int moe_combine_launcher(cab_bf16* out, const cab_bf16* y, const int* dst_row, const float* weights,
+                         const cab_bf16* extra, int T, int H, int k, int config,
+                         cab_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

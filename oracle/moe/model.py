@@ -1,0 +1,243 @@
+"""Eager oracle for the FP8 block-scaled MoE layer (TEST INFRASTRUCTURE).
+
+File shape follows the reference's eager-model slot (agent_workdir/model.py:9-26):
+``Model``, ``get_inputs()`` (CPU tensors), ``get_init_inputs()``. The reference
+ships no MoE model, test or vector, so parity of this path is UNPINNED by the
+reference; this file restates the operator definition, and the tests pin it with
+float64 loops, e4m3 known-answer values and committed fixtures.
+
+Pipeline (T tokens, hidden H, expert intermediate I, E experts, top-k):
+
+  logits = x @ Wr^T                       bf16 inputs, fp32 result              [T, E]
+  routing "softmax"  : the k largest logits, descending, ties -> lower expert id
+                       (the same order as the softmax values in exact arithmetic);
+                       weights = softmax restricted to the chosen k (that is the
+                       softmax renormalised to sum 1)
+  routing "sigmoid"  : s = sigmoid(logits) computed in float64 and rounded to fp32;
+                       c = s + bias; group score = sum of the 2 largest c in each of
+                       n_group contiguous groups; keep the topk_group best groups
+                       (ties -> lower group); the k largest c inside kept groups
+                       (ties -> lower expert id); weights = s[idx] / sum(s[idx]) *
+                       routed_scaling_factor
+  xq, sx = quant_1x128(x)                  e4m3 + fp32 scale per token per 128 columns
+  perm   = stable sort of the flat (token, slot) list by expert id
+  per expert e, rows r of e:
+      gu = (xq*sx)[r] @ (W13q*S13)[e]^T    fp32; W13 rows [0,I) = gate, [I,2I) = up
+      h  = silu(gate) * up                 fp32
+      hq, sh = quant_1x128(h)              the re-quantisation is part of the definition
+      y  = (hq*sh) @ (W2q*S2)[e]^T         fp32 -> bf16
+  out[t] = sum over slots (ascending) of w[t,slot] * y[t,slot]   fp32 -> bf16
+  (+ shared expert: the same FFN with its own weights on every token, added in fp32)
+
+Quantisation rule (activations 1x128, weights 128x128): amax = max|v| over the
+block, floored at 1e-4; scale = amax / 448 (fp32 division); q = e4m3 round-to-
+nearest-even of v / scale (fp32 division), saturating at +-448.
+
+Choices this file makes where the task statement is silent: logits stay fp32;
+W13 is stored [gate; up]; the routed scaling factor defaults to 1.0; the routing
+bias is N(0, 0.02) from the model seed; all-equal logits pick experts 0..k-1.
+
+``CAB_MOE_CONFIG`` selects the shape: 0 and 1 are CPU-sized stand-ins for 3 and
+4; 3 = 4096 tokens, H 2048, I 1024, 64 experts, top-6 softmax; 4 = 8192 tokens,
+H 7168, I 2048, 256 experts, top-8 sigmoid with 8 groups / top-4 and one shared
+expert (the single-GPU form of the expert-parallel layer).
+"""
+import os
+
+import torch
+import torch.nn as nn
+
+FP8_MAX = 448.0
+AMAX_FLOOR = 1e-4
+BLK = 128
+
+CONFIGS = {
+    0: dict(T=96, H=256, I=128, E=8, k=2, routing="softmax", n_group=1, topk_group=1, shared=False),
+    1: dict(T=80, H=256, I=256, E=16, k=4, routing="sigmoid", n_group=4, topk_group=2, shared=True),
+    3: dict(T=4096, H=2048, I=1024, E=64, k=6, routing="softmax", n_group=1, topk_group=1, shared=False),
+    4: dict(T=8192, H=7168, I=2048, E=256, k=8, routing="sigmoid", n_group=8, topk_group=4, shared=True),
+}
+CONFIG = int(os.environ.get("CAB_MOE_CONFIG", "0"))
+
+# Model.forward returns the layer output only; rel-L2 2e-2 against this oracle.
+OUTPUT_POLICY = ("rel_l2", 2e-2)
+
+
+# ----------------------------------------------------------------------------- quantisation
+def quant_1x128(v: torch.Tensor):
+    """v fp32 [R, C] (C % 128 == 0) -> (q float8_e4m3fn [R, C], scale fp32 [R, C/128])."""
+    R, C = v.shape
+    blocks = v.float().reshape(R, C // BLK, BLK)
+    amax = blocks.abs().amax(dim=-1).clamp_min(AMAX_FLOOR)
+    scale = amax / FP8_MAX
+    q = (blocks / scale[..., None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(R, C), scale
+
+
+def dequant_1x128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    R, C = q.shape
+    return (q.float().reshape(R, C // BLK, BLK) * scale[..., None]).reshape(R, C)
+
+
+def quant_128x128(w: torch.Tensor):
+    """w fp32 [..., N, K] (both % 128 == 0) -> (q e4m3 same shape, scale fp32 [..., N/128, K/128])."""
+    *lead, N, K = w.shape
+    blocks = w.float().reshape(*lead, N // BLK, BLK, K // BLK, BLK)
+    amax = blocks.abs().amax(dim=(-3, -1)).clamp_min(AMAX_FLOOR)
+    scale = amax / FP8_MAX
+    q = (blocks / scale[..., :, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(*lead, N, K), scale
+
+
+def dequant_128x128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    *lead, N, K = q.shape
+    blocks = q.float().reshape(*lead, N // BLK, BLK, K // BLK, BLK)
+    return (blocks * scale[..., :, None, :, None]).reshape(*lead, N, K)
+
+
+# ----------------------------------------------------------------------------- routing
+def topk_stable(values: torch.Tensor, k: int) -> torch.Tensor:
+    """Indices of the k largest per row, descending, ties broken toward the lower index."""
+    order = torch.sort(values, dim=-1, descending=True, stable=True).indices
+    return order[..., :k]
+
+
+def route_softmax_topk(logits: torch.Tensor, k: int):
+    idx = topk_stable(logits.float(), k)
+    chosen = torch.gather(logits.float(), -1, idx)
+    w = torch.softmax(chosen, dim=-1)
+    return idx.to(torch.int32), w
+
+
+def sigmoid_f64_to_f32(logits: torch.Tensor) -> torch.Tensor:
+    return torch.sigmoid(logits.double()).float()
+
+
+def route_sigmoid_group_topk(logits, bias, k, n_group, topk_group, routed_scaling_factor=1.0):
+    T, E = logits.shape
+    s = sigmoid_f64_to_f32(logits)
+    c = s + bias.float()[None, :]
+    per_group = c.reshape(T, n_group, E // n_group)
+    top2 = torch.sort(per_group, dim=-1, descending=True, stable=True).values[..., :2]
+    group_score = top2[..., 0] + top2[..., 1]
+    keep = topk_stable(group_score, topk_group)                         # [T, topk_group]
+    mask = torch.zeros(T, n_group, dtype=torch.bool)
+    mask.scatter_(1, keep, True)
+    masked = torch.where(mask[..., None].expand_as(per_group), per_group,
+                         torch.full_like(per_group, float("-inf"))).reshape(T, E)
+    idx = topk_stable(masked, k)
+    chosen = torch.gather(s, -1, idx)
+    w = chosen / chosen.sum(dim=-1, keepdim=True) * routed_scaling_factor
+    return idx.to(torch.int32), w
+
+
+def permutation(idx: torch.Tensor, E: int):
+    """Stable sort of the flat (token, slot) list by expert.
+
+    Returns perm [T*k] (perm[p] = flat index t*k+slot of the p-th sorted entry),
+    inv_perm [T*k] (position of flat entry i) and counts [E], all int32."""
+    flat = idx.reshape(-1).long()
+    perm = torch.sort(flat, stable=True).indices
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(perm.numel())
+    counts = torch.bincount(flat, minlength=E)
+    return perm.to(torch.int32), inv.to(torch.int32), counts.to(torch.int32)
+
+
+# ----------------------------------------------------------------------------- FFN
+def expert_ffn(xq, sx, w13_q, w13_s, w2_q, w2_s):
+    """SwiGLU FFN of one expert on already-quantised rows; returns y fp32 [R, H]."""
+    I = w2_q.shape[-1]
+    a = dequant_1x128(xq, sx)
+    gu = a @ dequant_128x128(w13_q, w13_s).t()
+    h = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    hq, sh = quant_1x128(h)
+    return dequant_1x128(hq, sh) @ dequant_128x128(w2_q, w2_s).t()
+
+
+class Model(nn.Module):
+    """forward(x bf16 [T, H]) -> out bf16 [T, H]."""
+
+    def __init__(self, T, H, I, E, k, routing="softmax", n_group=1, topk_group=1, shared=False,
+                 routed_scaling_factor=1.0, seed=4321):
+        super().__init__()
+        assert H % BLK == 0 and I % BLK == 0 and E % n_group == 0
+        self.T, self.H, self.I, self.E, self.k = T, H, I, E, k
+        self.routing, self.n_group, self.topk_group = routing, n_group, topk_group
+        self.routed_scaling_factor = routed_scaling_factor
+        gen = torch.Generator().manual_seed(seed)
+        self.router_w = nn.Parameter((torch.randn(E, H, generator=gen) * 0.02).to(torch.bfloat16),
+                                     requires_grad=False)
+        self.register_buffer("router_bias", torch.randn(E, generator=gen) * 0.02)
+        w13_q = torch.empty(E, 2 * I, H, dtype=torch.float8_e4m3fn)
+        w13_s = torch.empty(E, 2 * I // BLK, H // BLK)
+        w2_q = torch.empty(E, H, I, dtype=torch.float8_e4m3fn)
+        w2_s = torch.empty(E, H // BLK, I // BLK)
+        for e in range(E):  # one expert at a time keeps the fp32 staging small
+            w13_q[e], w13_s[e] = quant_128x128(torch.randn(2 * I, H, generator=gen) * 0.02)
+            w2_q[e], w2_s[e] = quant_128x128(torch.randn(H, I, generator=gen) * 0.02)
+        for name, t in (("w13_q", w13_q), ("w13_s", w13_s), ("w2_q", w2_q), ("w2_s", w2_s)):
+            self.register_buffer(name, t)
+        self.has_shared = bool(shared)
+        if shared:
+            q, s = quant_128x128(torch.randn(2 * I, H, generator=gen) * 0.02)
+            self.register_buffer("shared_w13_q", q)
+            self.register_buffer("shared_w13_s", s)
+            q, s = quant_128x128(torch.randn(H, I, generator=gen) * 0.02)
+            self.register_buffer("shared_w2_q", q)
+            self.register_buffer("shared_w2_s", s)
+
+    # pieces, exposed so that each kernel can be checked on its own
+    def logits(self, x):
+        return x.float() @ self.router_w.float().t()
+
+    def route(self, logits):
+        if self.routing == "softmax":
+            return route_softmax_topk(logits, self.k)
+        return route_sigmoid_group_topk(logits, self.router_bias, self.k, self.n_group,
+                                        self.topk_group, self.routed_scaling_factor)
+
+    def forward(self, x):
+        T, H = x.shape
+        idx, w = self.route(self.logits(x))
+        xq, sx = quant_1x128(x.float())
+        perm, inv_perm, counts = permutation(idx, self.E)
+        token_of = (perm.long() // self.k)
+        y = torch.empty(T * self.k, H, dtype=torch.bfloat16)          # in sorted order
+        start = 0
+        for e in range(self.E):
+            n = int(counts[e])
+            if n:
+                rows = token_of[start:start + n]
+                y[start:start + n] = expert_ffn(xq[rows], sx[rows], self.w13_q[e], self.w13_s[e],
+                                                self.w2_q[e], self.w2_s[e]).to(torch.bfloat16)
+            start += n
+        y_slots = y[inv_perm.long()].reshape(T, self.k, H).float()    # back to (token, slot)
+        out = torch.zeros(T, H)
+        for slot in range(self.k):                                    # ascending slot order
+            out = out + w[:, slot, None] * y_slots[:, slot]
+        if self.has_shared:
+            out = out + expert_ffn(xq, sx, self.shared_w13_q, self.shared_w13_s, self.shared_w2_q,
+                                   self.shared_w2_s).to(torch.bfloat16).float()
+        return out.to(torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- inputs
+_GEN = None
+
+
+def reseed(seed=None) -> None:
+    global _GEN
+    _GEN = torch.Generator().manual_seed(1234 + CONFIG if seed is None else seed)
+
+
+def get_inputs():
+    if _GEN is None:
+        reseed()
+    c = CONFIGS[CONFIG]
+    return [torch.randn(c["T"], c["H"], generator=_GEN).to(torch.bfloat16)]
+
+
+def get_init_inputs():
+    c = CONFIGS[CONFIG]
+    return [c["T"], c["H"], c["I"], c["E"], c["k"], c["routing"], c["n_group"], c["topk_group"], c["shared"]]
