@@ -27,6 +27,7 @@ SIGNATURES = {
     "moe_permute_launcher": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p]),
     "moe_quant_dispatch_launcher": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
     "moe_combine_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),
+    "moe_grouped_gemm_fp8_launcher": (c_int, [c_int] + [c_void_p] * 8 + [c_int] * 6 + [c_void_p, c_int, c_void_p]),
 }
 
 
@@ -150,3 +151,16 @@ def moe_combine(out, y, dst_row, weights, extra=None, config: int = 0) -> None:
     _check("moe_combine_launcher",
            lib().moe_combine_launcher(_p(out), _p(y), _p(dst_row), _p(weights), _opt(extra), T, H,
                                       weights.shape[1], config, _stream()))
+
+
+def moe_grouped_gemm_fp8(mode, out, out_scales_t, a_q, a_scales_t, w_q, w_scales, tile_expert, num_tiles,
+                         max_m_tiles, status=None, config: int = 0) -> None:
+    """mode 0: gate/up + SwiGLU + re-quantise; mode 1: down projection to bf16 (see the header)."""
+    rows_cap, K = a_q.shape
+    E = w_q.shape[0]
+    N = out.shape[1]
+    _check("moe_grouped_gemm_fp8_launcher",
+           lib().moe_grouped_gemm_fp8_launcher(mode, _p(out), _opt(out_scales_t), _p(a_q), _p(a_scales_t),
+                                               _p(w_q), _p(w_scales), _opt(tile_expert), _opt(num_tiles),
+                                               max_m_tiles, rows_cap, a_scales_t.shape[1], E, N, K,
+                                               _opt(status), config, _stream()))

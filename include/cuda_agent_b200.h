@@ -156,6 +156,28 @@ int moe_combine_launcher(cab_bf16* out, const cab_bf16* y, const int* dst_row, c
                          const cab_bf16* extra, int T, int H, int k, int config,
                          cab_stream_t stream);
 
+/* Grouped FP8 GEMM with fp32 block scales on tcgen05 / TMEM / TMA.               */
+/*   C[m, n] = sum over 128-wide K blocks kb of                                   */
+/*             a_scales_t[kb, m] * w_scales[e, n/128, kb] * (a_q[m, kb] . w_q[e, n, kb])  */
+/* where e = tile_expert[m / 128] (rows live in the padded row space of            */
+/* moe_permute_launcher; tile_expert == num_tiles == NULL means one dense expert   */
+/* over max_m_tiles tiles and needs E == 1).                                       */
+/*   mode 0: w_q = W13 e4m3 [E, 2N, K] (rows [0,N) gate, [N,2N) up), w_scales       */
+/*           [E, 2N/128, K/128]; h = silu(gate) * up is re-quantised 1x128 and      */
+/*           written to out (e4m3 [rows_cap, N]) and out_scales_t ([N/128,ld_rows]).*/
+/*           N % 128 == 0.                                                          */
+/*   mode 1: w_q = W2 e4m3 [E, N, K], w_scales [E, N/128, K/128]; out = bf16         */
+/*           [rows_cap, N]; out_scales_t unused. N % 256 == 0.                       */
+/* a_q: e4m3 [rows_cap, K]; a_scales_t: fp32 [K/128, ld_rows]; K % 128 == 0;         */
+/* rows_cap >= 128 * max_m_tiles; ld_rows >= rows_cap. status (device int, may be    */
+/* NULL) is cleared, then set non-zero if a bounded wait inside the kernel gave up.  */
+/* config > 0 overrides the number of persistent CTAs (default: one per SM).         */
+int moe_grouped_gemm_fp8_launcher(int mode, void* out, float* out_scales_t, const cab_e4m3* a_q,
+                                  const float* a_scales_t, const cab_e4m3* w_q, const float* w_scales,
+                                  const int* tile_expert, const int* num_tiles, int max_m_tiles,
+                                  int rows_cap, int ld_rows, int E, int N, int K, int* status,
+                                  int config, cab_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif
