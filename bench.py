@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--config", type=int, default=0, help="launcher variant passed to the op")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", choices=["gdn", "moe"], default="gdn",
+                    help="gdn = the headline line; moe = FP8 MoE layer (4096 tokens, 64 experts, top-6)")
     return ap.parse_args()
 
 
@@ -363,8 +365,65 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_moe(args):
+    """Secondary line: the FP8 MoE layer of 4096 tokens (hidden 2048, intermediate 1024, 64 experts, top-6).
+
+    value = grouped-GEMM FLOP (6*T*k*H*I) / time of the two grouped GEMM kernels; e2e = the same FLOP
+    over the whole layer through cuda_extension.moe_forward with x coming from pinned host memory and
+    the output going back. Weights (403 MB) exceed L2, so no flush is needed between steps."""
+    import torch
+    from cuda_agent_b200.benchmarks import MoeWorkload, time_cuda
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    wl = MoeWorkload(dev)
+    steps, warmup = min(args.steps, 200), max(3, min(args.warmup, 20))
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    w0 = time.monotonic()
+    ms_gemm = time_cuda(lambda: wl.gemm_step(args.config), steps, warmup)
+    ms_layer = time_cuda(lambda: wl.layer_step(config=args.config), steps, warmup)
+    hx = wl.x.cpu().pin_memory()
+    ho = torch.empty_like(hx).pin_memory()
+    dx = torch.empty_like(wl.x)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        ho.copy_(wl.layer_step(dx, args.config), non_blocking=True)
+    ms_e2e = time_cuda(e2e_step, steps, warmup)
+    windows = [(w0, time.monotonic())]
+    sampler.stop()
+    assert wl.status.cpu().tolist() == [0, 0]
+    tflops = wl.gemm_flops / (ms_gemm * 1e-3) / 1e12
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peak = 2.0 * float(json.loads(peaks_file.read_text())["bf16_tflops"])
+        src = "2 x measured bf16 burst (MEASURED_PEAKS.json bf16_tflops); nominal fp8 dense 4500"
+    else:
+        peak, src = 2.0 * 1590.0, "2 x fallback bf16 1590; nominal fp8 dense 4500"
+    line = {
+        "metric": "moe_fp8_grouped_gemm_tflops", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms_gemm, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+        "config": {"workload": "moe_fp8_layer", "T": wl.T, "H": wl.H, "I": wl.I, "E": wl.E, "k": wl.k,
+                   "gemm_flops": wl.gemm_flops, "min_bytes": wl.min_bytes,
+                   "l2": "expert weights (403 MB) exceed L2 (126 MB); no flush needed"},
+        "layer_ms": round(ms_layer, 5),
+        "e2e": {"value": round(wl.gemm_flops / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2,
+                "ms_per_step": round(ms_e2e, 5), "api": "cuda_extension.moe_forward"},
+        "gpu_launches": 2 * steps,
+        "roofline": {"bound": "tensor", "kernel": "moe_gemm_fp8_kernel<0> + <1>", "achieved": round(tflops, 2),
+                     "peak": peak, "unit": "TFLOP/s", "frac": round(tflops / peak, 4), "traffic": None,
+                     "peak_source": src},
+        "clocks": sampler.summary(windows),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.workload == "moe" and args.impl != "reference":
+        return run_moe(args)
     if args.impl == "reference":
         run_reference(args)
     else:

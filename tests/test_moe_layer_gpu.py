@@ -1,0 +1,86 @@
+"""The MoE layer end to end on the GPU: extension op and reference-style verification loop.
+
+Tolerance (stated for this path): rel-L2 <= 2e-2 against the oracle's dequantised
+matmul; expert indices identical wherever the oracle's own top-(k+1) logits are
+separated by more than fp32 summation noise (1e-4), which the test counts.
+"""
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT, load_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def to_dev(model, dev):
+    return {k: v.to(dev) for k, v in model.state_dict().items()}
+
+
+def run_layer(ext, model, sd, x, check=True):
+    sh = [sd.get(n) for n in ("shared_w13_q", "shared_w13_s", "shared_w2_q", "shared_w2_s")]
+    return ext.moe_forward(x, sd["router_w"], sd["router_bias"], sd["w13_q"], sd["w13_s"], sd["w2_q"], sd["w2_s"],
+                           *sh, model.k, 0 if model.routing == "softmax" else 1, model.n_group, model.topk_group,
+                           model.routed_scaling_factor, check, 0)
+
+
+@pytest.mark.parametrize("cfg", [0, 1])
+def test_verification_loop(cuda_device, built_libs, capsys, cfg):
+    import os
+    os.environ["CAB_MOE_CONFIG"] = str(cfg)
+    sys.path.insert(0, str(built_libs.WORKDIR))
+    from utils import verification
+    rc = verification.main(["--task", str(built_libs.WORKDIR / "tasks" / "moe"),
+                            "--model-dir", str(ROOT / "oracle" / "moe")])
+    assert rc == 0
+    assert "[PASS] verify success" in capsys.readouterr().out
+
+
+@pytest.mark.parametrize("cfg,T", [(0, 96), (1, 80), (1, 1), (0, 129)])
+def test_layer_and_routing_match_oracle(cuda_device, cfg, T):
+    import cuda_agent_b200
+    ext = cuda_agent_b200.load_extension()
+    m = load_oracle("moe", {"CAB_MOE_CONFIG": cfg})
+    args = m.get_init_inputs()
+    args[0] = T
+    model = m.Model(*args)
+    sd = to_dev(model, cuda_device)
+    gen = torch.Generator().manual_seed(T)
+    x = torch.randn(T, model.H, generator=gen).to(torch.bfloat16)
+    ref = model(x)
+    out = run_layer(ext, model, sd, x.to(cuda_device))
+    rel = float((out.float().cpu() - ref.float()).norm() / ref.float().norm())
+    assert rel <= 2e-2, rel
+    idx, w = ext.moe_route(x.to(cuda_device), sd["router_w"], sd["router_bias"], model.k,
+                           0 if model.routing == "softmax" else 1, model.n_group, model.topk_group, 1.0)
+    ref_idx, ref_w = model.route(model.logits(x))
+    assert torch.equal(idx.cpu(), ref_idx)
+    torch.testing.assert_close(w.cpu(), ref_w, rtol=1e-4, atol=1e-6)
+
+
+def test_config3_full_size(cuda_device):
+    """4096 tokens, H 2048, I 1024, 64 experts, top-6: the layer output and every routing index."""
+    import cuda_agent_b200
+    ext = cuda_agent_b200.load_extension()
+    m = load_oracle("moe", {"CAB_MOE_CONFIG": 3})
+    m.reseed()
+    model = m.Model(*m.get_init_inputs())
+    sd = to_dev(model, cuda_device)
+    (x,) = m.get_inputs()
+    logits = model.logits(x)
+    ref_idx, _ = model.route(logits)
+    idx, _ = ext.moe_route(x.to(cuda_device), sd["router_w"], sd["router_bias"], model.k, 0, 1, 1, 1.0)
+    top = torch.sort(logits, dim=-1, descending=True).values[:, : model.k + 1]
+    safe = (top[:, :-1] - top[:, 1:]).min(dim=-1).values > 1e-4
+    assert int(safe.sum()) > 0.98 * len(safe)
+    assert torch.equal(idx.cpu()[safe], ref_idx[safe])
+    mismatched_tokens = int((idx.cpu() != ref_idx).any(dim=-1).sum())
+    assert mismatched_tokens <= int((~safe).sum())
+    ref = model(x)
+    out = run_layer(ext, model, sd, x.to(cuda_device))
+    rel = float((out.float().cpu() - ref.float()).norm() / ref.float().norm())
+    assert rel <= 2e-2, rel
+    # run-to-run determinism of the whole layer
+    out2 = run_layer(ext, model, sd, x.to(cuda_device))
+    assert torch.equal(out, out2)
