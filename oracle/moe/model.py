@@ -121,7 +121,7 @@ def route_sigmoid_group_topk(logits, bias, k, n_group, topk_group, routed_scalin
     top2 = torch.sort(per_group, dim=-1, descending=True, stable=True).values[..., :2]
     group_score = top2[..., 0] + top2[..., 1]
     keep = topk_stable(group_score, topk_group)                         # [T, topk_group]
-    mask = torch.zeros(T, n_group, dtype=torch.bool)
+    mask = torch.zeros(T, n_group, dtype=torch.bool, device=logits.device)
     mask.scatter_(1, keep, True)
     masked = torch.where(mask[..., None].expand_as(per_group), per_group,
                          torch.full_like(per_group, float("-inf"))).reshape(T, E)
@@ -139,7 +139,7 @@ def permutation(idx: torch.Tensor, E: int):
     flat = idx.reshape(-1).long()
     perm = torch.sort(flat, stable=True).indices
     inv = torch.empty_like(perm)
-    inv[perm] = torch.arange(perm.numel())
+    inv[perm] = torch.arange(perm.numel(), device=perm.device)
     counts = torch.bincount(flat, minlength=E)
     return perm.to(torch.int32), inv.to(torch.int32), counts.to(torch.int32)
 
@@ -203,7 +203,7 @@ class Model(nn.Module):
         xq, sx = quant_1x128(x.float())
         perm, inv_perm, counts = permutation(idx, self.E)
         token_of = (perm.long() // self.k)
-        y = torch.empty(T * self.k, H, dtype=torch.bfloat16)          # in sorted order
+        y = torch.empty(T * self.k, H, dtype=torch.bfloat16, device=x.device)   # in sorted order
         start = 0
         for e in range(self.E):
             n = int(counts[e])
@@ -213,7 +213,7 @@ class Model(nn.Module):
                                                 self.w2_q[e], self.w2_s[e]).to(torch.bfloat16)
             start += n
         y_slots = y[inv_perm.long()].reshape(T, self.k, H).float()    # back to (token, slot)
-        out = torch.zeros(T, H)
+        out = torch.zeros(T, H, device=x.device)
         for slot in range(self.k):                                    # ascending slot order
             out = out + w[:, slot, None] * y_slots[:, slot]
         if self.has_shared:
