@@ -60,8 +60,10 @@ def parse_args():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--config", type=int, default=0, help="launcher variant passed to the op")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["gdn", "moe"], default="gdn",
-                    help="gdn = the headline line; moe = FP8 MoE layer (4096 tokens, 64 experts, top-6)")
+    ap.add_argument("--workload", choices=["gdn", "moe", "mla"], default="gdn",
+                    help="gdn = the headline line; moe = FP8 MoE layer (4096 tokens, 64 experts, top-6); "
+                         "mla = top-2048 sparse MLA decode (64 sequences, 128 heads)")
+    ap.add_argument("--nsplit", type=int, default=1, help="mla: splits of the selected rows per CTA group")
     return ap.parse_args()
 
 
@@ -420,10 +422,65 @@ def run_moe(args):
     print(json.dumps(line), flush=True)
 
 
+def run_mla(args):
+    """Secondary line: sparse MLA decode, 64 sequences x 128 heads, 2048 selected rows of a 2.4 GB cache.
+
+    value = sequences (one new token each) per second with everything in HBM; e2e = the same through
+    cuda_extension.mla_sparse_decode_forward with q / idx / seq_len from pinned host memory and the output
+    back (the KV cache is resident, as in serving). The cache (2.4 GB) exceeds L2; the 2048 rows a step
+    touches per sequence are 151 MB in total, also above L2, so no flush is needed."""
+    import torch
+    from cuda_agent_b200.benchmarks import MlaWorkload, time_cuda
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    wl = MlaWorkload(dev)
+    steps, warmup = min(args.steps, 200), max(3, min(args.warmup, 20))
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    w0 = time.monotonic()
+    ms = time_cuda(lambda: wl.step(args.nsplit, args.config), steps, warmup)
+    hq, hidx, hlen = wl.q.cpu().pin_memory(), wl.idx.cpu().pin_memory(), wl.seq_len.cpu().pin_memory()
+    ho = torch.empty(wl.out.shape, dtype=torch.bfloat16).pin_memory()
+    dq, didx, dlen = torch.empty_like(wl.q), torch.empty_like(wl.idx), torch.empty_like(wl.seq_len)
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True); didx.copy_(hidx, non_blocking=True); dlen.copy_(hlen, non_blocking=True)
+        ho.copy_(wl.api_step(dq, didx, dlen), non_blocking=True)
+    ms_e2e = time_cuda(e2e_step, steps, warmup)
+    windows = [(w0, time.monotonic())]
+    sampler.stop()
+    assert int(wl.status) == 0
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0}
+    t_roof = max(wl.bytes / (peaks["hbm_gbs"] * 1e9), wl.flops / (peaks["bf16_tflops"] * 1e12))
+    gbs = wl.bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "sparse_mla_decode_tok_per_s", "value": round(wl.B / (ms * 1e-3), 1), "unit": "tok/s", "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 (fp32 softmax and accumulation)", "data": "synthetic",
+        "config": {"workload": "sparse_mla_decode", "B": wl.B, "heads": wl.Hh, "S": wl.S, "topk": wl.topk,
+                   "nsplit": args.nsplit, "bytes": wl.bytes, "flops": wl.flops,
+                   "l2": "rows touched per step (151 MB) and the cache (2.4 GB) exceed L2; no flush needed"},
+        "e2e": {"value": round(wl.B / (ms_e2e * 1e-3), 1), "unit": "tok/s",
+                "h2d_bytes_per_step": hq.numel() * 2 + hidx.numel() * 4 + hlen.numel() * 4,
+                "d2h_bytes_per_step": ho.numel() * 2, "ms_per_step": round(ms_e2e, 5),
+                "api": "cuda_extension.mla_sparse_decode_forward"},
+        "gpu_launches": steps * (1 if args.nsplit == 1 else 2),
+        "roofline": {"bound": "hbm", "kernel": "mla_sparse_decode_kernel", "achieved": round(gbs, 1),
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None,
+                     "roofline_time_us": round(t_roof * 1e6, 2), "frac_of_roofline_time": round(t_roof / (ms * 1e-3), 4),
+                     "peak_source": "MEASURED_PEAKS.json (hbm_gbs; bf16_tflops for the compute side)"},
+        "clocks": sampler.summary(windows),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.workload == "moe" and args.impl != "reference":
         return run_moe(args)
+    if args.workload == "mla" and args.impl != "reference":
+        return run_mla(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -1,0 +1,477 @@
+// Top-k sparse MLA decode attention for sm_100a (absorbed latent attention, one query
+// token per sequence): out[b,h,:] = softmax_j(q[b,h,:] . kv[b, idx[b,j], :] * scale) . kv[b, idx[b,j], :512]
+// over the valid entries of idx (0 <= idx < seq_len[b]).
+//
+// One CTA handles 64 query heads of one sequence and one contiguous range ("split") of the
+// selected rows, 64 rows at a time:
+//   producer warps (4)  gather the 64 selected cache rows (1152 B each) into shared memory with
+//                       16-byte cp.async copies, laid out as nine 64-row x 128-byte tiles in the
+//                       128-byte swizzle the tensor core reads; two stages
+//   MMA warp (1 thread) S = Q . K^T   : tcgen05.mma kind::f16, M=64 N=64, 36 steps of K=16
+//                       O += P . V    : V is the first 512 columns of the same tile read as an
+//                                       MN-major operand, two M=64 N=256 accumulators that share
+//                                       256 tensor-memory columns (lanes 0-15 / 16-31 of each quadrant)
+//                       per block the order is Q.K^T, (softmax), P.V: the stage is released as early
+//                       as possible, the gather of the block after next overlaps the next block
+//   softmax warps (4)   read S from tensor memory (one head per thread, lanes 0-15 of each warp),
+//                       scale, mask invalid entries, online softmax in the exp2 domain with a lazy
+//                       reference maximum (O is rescaled in tensor memory only when the running
+//                       maximum grows by more than 2^8), write P as bf16 into shared memory
+// All mbarrier waits are bounded. With nsplit > 1 the CTAs write unnormalised fp32 partials
+// plus (reference maximum, sum) and a second kernel merges them.
+#include "cab_common.cuh"
+#include "sm100_primitives.cuh"
+
+namespace {
+
+constexpr int kDqk = 576, kDv = 512;
+constexpr int kHeads = 64;                 // heads per CTA (UMMA M)
+constexpr int kTok = 64;                   // selected rows per block (UMMA N of QK, K of PV)
+constexpr int kChunks = kDqk / 64;         // 9 tiles of 64 columns
+constexpr int kChunkBytes = 64 * 128;      // 64 rows x 128 bytes
+constexpr int kTileBytes = kChunks * kChunkBytes;   // 73728: Q (64 heads) or one K stage (64 rows)
+constexpr int kPBytes = kHeads * 128;      // P: 64 heads x 64 tokens bf16
+constexpr int kProducerThreads = 128;
+constexpr int kThreads = 9 * 32;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 128;
+constexpr float kRescaleThreshold = 8.f;   // log2 units
+
+struct __align__(16) Control {
+  uint64_t kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_done;
+  uint32_t tmem_base;
+  int abort_flag;
+  unsigned char valid[2][kTok];
+};
+constexpr int kSmemBytes = 3 * kTileBytes + kPBytes + (int)sizeof(Control) + 1024;
+
+struct MlaParams {
+  const __nv_bfloat16* q;      // [B, 1, Hh, 576]
+  const __nv_bfloat16* kv;     // [B, S, 576]
+  const int* seq_len;          // [B]
+  const int* idx;              // [B, 1, topk]
+  __nv_bfloat16* out;          // [B, 1, Hh, 512]                 (nsplit == 1)
+  float* part_o;               // [B, nsplit, Hh, 512] unnormalised (nsplit > 1)
+  float* part_ml;              // [B, nsplit, Hh, 2]  (reference max in log2 units, sum)
+  int Hh, S, topk, nsplit;
+  float scale_log2;            // softmax scale * log2(e)
+  int* status;
+};
+
+enum { kWaitKvFull = 201, kWaitKvEmpty = 202, kWaitSFull = 203, kWaitSEmpty = 204, kWaitPFull = 205,
+       kWaitPEmpty = 206, kWaitODone = 207 };
+
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Operand descriptor for 128-byte-swizzled tiles; offsets in bytes.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Copies `rows` x 576 bf16 (16-byte pieces, coalesced per row) into the nine swizzled tiles at `dst`.
+// `src_row(r)` yields the global pointer of row r.
+template <typename RowPtr>
+__device__ __forceinline__ void gather_tile(uint32_t dst, int tid, int nthreads, RowPtr src_row) {
+  for (int id = tid; id < kTok * 72; id += nthreads) {
+    const int r = id / 72, c16 = id - r * 72;
+    const int chunk = c16 >> 3, within = c16 & 7;
+    cp_async_16(dst + chunk * kChunkBytes + r * 128 + ((within ^ (r & 7)) << 4), src_row(r) + c16 * 8);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const MlaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_tile = base;
+  uint8_t* kv_tile = base + kTileBytes;              // two stages
+  uint8_t* p_tile = base + 3 * kTileBytes;
+  Control& ctl = *reinterpret_cast<Control*>(p_tile + kPBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head0 = blockIdx.x * kHeads, split = blockIdx.y, b = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      sm100::mbar_init(&ctl.kv_full[s], kProducerThreads);
+      sm100::mbar_init(&ctl.kv_empty[s], 1);
+      sm100::mbar_init(&ctl.s_full[s], 1);
+      sm100::mbar_init(&ctl.s_empty[s], 4);
+    }
+    sm100::mbar_init(&ctl.p_full, 4);
+    sm100::mbar_init(&ctl.p_empty, 1);
+    sm100::mbar_init(&ctl.o_done, 1);
+    ctl.abort_flag = 0;
+    sm100::mbar_fence_init();
+  }
+  if (warp == 4) {
+    sm100::tmem_alloc(&ctl.tmem_base, kTmemCols);
+    sm100::tmem_relinquish();
+  }
+  // Q tile: 64 heads x 576, every thread helps
+  {
+    const __nv_bfloat16* qb = p.q + ((size_t)b * p.Hh + head0) * kDqk;
+    gather_tile(sm100::smem_u32(q_tile), threadIdx.x, kThreads,
+                [&](int r) { return qb + (size_t)r * kDqk; });
+    cp_async_commit();
+    cp_async_wait<0>();
+    sm100::fence_proxy_async();
+  }
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  sm100::tc_fence_after_sync();
+  const uint32_t tmem_base = ctl.tmem_base;
+  volatile int* abort_flag = &ctl.abort_flag;
+
+  const int blocks_total = (p.topk + kTok - 1) / kTok;
+  const int per_split = (blocks_total + p.nsplit - 1) / p.nsplit;
+  const int j0 = split * per_split;
+  const int nb = max(0, min(blocks_total, j0 + per_split) - j0);
+  const int len = __ldg(p.seq_len + b);
+
+  if (warp >= 5) {
+    // ---------------------------------------------------------------- producers
+    const int ptid = threadIdx.x - 5 * 32;
+    const int* idx_b = p.idx + (size_t)b * p.topk;
+    const __nv_bfloat16* kv_b = p.kv + (size_t)b * p.S * kDqk;
+    for (int j = 0; j < nb + 1; ++j) {
+      if (j < nb) {
+        const int st = j & 1;
+        if (j >= 2 && !sm100::mbar_wait_relaxed(&ctl.kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kWaitKvEmpty))
+          break;
+        const int tok0 = (j0 + j) * kTok;
+        if (ptid < kTok) {
+          const int i = tok0 + ptid;
+          const int t = i < p.topk ? __ldg(idx_b + i) : -1;
+          ctl.valid[st][ptid] = (t >= 0 && t < len) ? 1 : 0;
+        }
+        gather_tile(sm100::smem_u32(kv_tile + st * kTileBytes), ptid, kProducerThreads, [&](int r) {
+          const int i = tok0 + r;
+          const int t = i < p.topk ? __ldg(idx_b + i) : -1;
+          // an invalid entry copies row 0: finite data that the mask multiplies by zero
+          return kv_b + (size_t)((t >= 0 && t < len) ? t : 0) * kDqk;
+        });
+      }
+      cp_async_commit();
+      if (j >= 1) {
+        // block j-1 has landed: make it visible to the tensor core and publish it
+        cp_async_wait<1>();
+        sm100::fence_proxy_async();
+        sm100::mbar_arrive(&ctl.kv_full[(j - 1) & 1]);
+      }
+    }
+  } else if (warp == 4) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = sm100::umma_idesc(1 /* bf16 */, kHeads, kTok);
+      constexpr uint32_t idesc_pv = sm100::umma_idesc(1, kHeads, 256) | (1u << 16);   // B is MN-major
+      const uint32_t q_addr = sm100::smem_u32(q_tile), p_addr = sm100::smem_u32(p_tile);
+      bool ok = true;
+      auto issue_pv = [&](int i) {
+        const int st = i & 1;
+        if (!sm100::mbar_wait(&ctl.p_full, i & 1, abort_flag, p.status, kWaitPFull)) { ok = false; return; }
+        sm100::tc_fence_after_sync();
+        const uint32_t v_addr = sm100::smem_u32(kv_tile + st * kTileBytes);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t d = tmem_base + kColO + (half ? (16u << 16) : 0u);
+          const uint64_t a = umma_desc_sw128(p_addr, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(v_addr + half * 4 * kChunkBytes, kChunkBytes, 1024);
+#pragma unroll
+          for (int k4 = 0; k4 < kTok / 16; ++k4)   // 16 tokens per step: 32 B along P rows, 2 KiB down V
+            sm100::umma_f16(d, a + 2 * k4, bd + (uint64_t)k4 * (2048 >> 4), idesc_pv, (i > 0 || k4 > 0) ? 1u : 0u);
+        }
+        sm100::umma_commit(&ctl.kv_empty[st]);
+        sm100::umma_commit(&ctl.p_empty);
+      };
+      for (int j = 0; j < nb && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!sm100::mbar_wait(&ctl.kv_full[st], ph, abort_flag, p.status, kWaitKvFull)) { ok = false; break; }
+        if (!sm100::mbar_wait(&ctl.s_empty[st], ph ^ 1, abort_flag, p.status, kWaitSEmpty)) { ok = false; break; }
+        sm100::tc_fence_after_sync();
+        const uint32_t k_addr = sm100::smem_u32(kv_tile + st * kTileBytes);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          const uint64_t a = umma_desc_sw128(q_addr + c * kChunkBytes, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(k_addr + c * kChunkBytes, 16, 1024);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            sm100::umma_f16(tmem_base + kColS + st * kTok, a + 2 * k4, bd + 2 * k4, idesc_qk, (c > 0 || k4 > 0) ? 1u : 0u);
+        }
+        sm100::umma_commit(&ctl.s_full[st]);
+        // P.V of the same block follows at once: with two K/V stages the stage of block j can only be
+        // refilled after this P.V, so issuing it before the next Q.K^T is what lets the gather of
+        // block j+2 start while block j+1 is computed.
+        issue_pv(j);
+      }
+      if (ok) sm100::umma_commit(&ctl.o_done);
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue (warps 0..3)
+    const bool row_ok = lane < 16;                 // M=64 accumulators live in lanes 0-15 of each quadrant
+    const int head = head0 + warp * 16 + (lane & 15);
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      const int st = j & 1;
+      int got = 1;
+      if (lane == 0) got = sm100::mbar_wait(&ctl.s_full[st], (j >> 1) & 1, abort_flag, p.status, kWaitSFull);
+      if (!__shfl_sync(0xffffffffu, got, 0)) { ok = false; break; }
+      sm100::tc_fence_after_sync();
+      uint32_t t0[32], t1[32];
+      sm100::tmem_ld_32x32(lane_base + kColS + st * kTok, t0);
+      sm100::tmem_ld_32x32(lane_base + kColS + st * kTok + 32, t1);
+      sm100::tmem_ld_wait();
+      sm100::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&ctl.s_empty[st]);
+
+      float s[kTok];
+      float m_blk = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kTok; ++i) {
+        const float raw = __uint_as_float(i < 32 ? t0[i] : t1[i - 32]);
+        s[i] = (row_ok && ctl.valid[st][i]) ? raw * p.scale_log2 : -INFINITY;
+        m_blk = fmaxf(m_blk, s[i]);
+      }
+      // lazy reference maximum: move it only on the first non-empty block or on a jump > 2^8
+      float factor = 1.f;
+      if (m_blk > -INFINITY) {
+        if (m_ref == -INFINITY) {
+          m_ref = m_blk;
+        } else if (m_blk > m_ref + kRescaleThreshold) {
+          factor = exp2f(m_ref - m_blk);
+          m_ref = m_blk;
+        }
+      }
+      float psum = 0.f;
+      uint32_t packed[kTok / 2];
+#pragma unroll
+      for (int i = 0; i < kTok; i += 2) {
+        const float p0 = s[i] == -INFINITY ? 0.f : exp2f(s[i] - m_ref);
+        const float p1 = s[i + 1] == -INFINITY ? 0.f : exp2f(s[i + 1] - m_ref);
+        psum += p0 + p1;
+        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+      }
+      l_sum = l_sum * factor + psum;
+
+      // P and O may be touched only after the previous P.V has finished
+      if (j > 0) {
+        got = 1;
+        if (lane == 0) got = sm100::mbar_wait(&ctl.p_empty, (j - 1) & 1, abort_flag, p.status, kWaitPEmpty);
+        if (!__shfl_sync(0xffffffffu, got, 0)) { ok = false; break; }
+        sm100::tc_fence_after_sync();
+      }
+      // lanes 16-31 hold the upper 256 output columns of the row owned by lane - 16
+      const float my_factor = __shfl_sync(0xffffffffu, factor, lane & 15);
+      if (__any_sync(0xffffffffu, my_factor != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t o[32];
+          sm100::tmem_ld_32x32(lane_base + kColO + c, o);
+          sm100::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * my_factor);
+          tmem_st_32x32(lane_base + kColO + c, o);
+        }
+        tmem_st_wait();
+      }
+      if (row_ok) {
+        const int r = warp * 16 + lane;
+        uint8_t* prow = p_tile + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
+              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
+      sm100::fence_proxy_async();
+      sm100::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&ctl.p_full);
+    }
+
+    // ------------------------------------------------------------ epilogue
+    if (ok) {
+      int got = 1;
+      if (lane == 0) got = sm100::mbar_wait(&ctl.o_done, 0, abort_flag, p.status, kWaitODone);
+      ok = __shfl_sync(0xffffffffu, got, 0) != 0;
+    }
+    if (ok) {
+      sm100::tc_fence_after_sync();
+      const float l_row = __shfl_sync(0xffffffffu, l_sum, lane & 15);
+      const float m_row = __shfl_sync(0xffffffffu, m_ref, lane & 15);
+      const int col0 = lane < 16 ? 0 : 256;
+      if (p.nsplit == 1) {
+        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+        __nv_bfloat16* dst = p.out + ((size_t)b * p.Hh + head) * kDv + col0;
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t o[32];
+          if (nb > 0) { sm100::tmem_ld_32x32(lane_base + kColO + c, o); sm100::tmem_ld_wait(); }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float a = nb > 0 ? __uint_as_float(o[8 * v + 2 * k]) * inv : 0.f;
+              const float bb = nb > 0 ? __uint_as_float(o[8 * v + 2 * k + 1]) * inv : 0.f;
+              __nv_bfloat162 pk = __floats2bfloat162_rn(l_row > 0.f ? a : 0.f, l_row > 0.f ? bb : 0.f);
+              w[k] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(dst + c + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      } else {
+        const size_t slot = ((size_t)b * p.nsplit + split) * p.Hh + head;
+        float* dst = p.part_o + slot * kDv + col0;
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t o[32];
+          if (nb > 0) { sm100::tmem_ld_32x32(lane_base + kColO + c, o); sm100::tmem_ld_wait(); }
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            float4 f;
+            f.x = (nb > 0 && l_row > 0.f) ? __uint_as_float(o[4 * v + 0]) : 0.f;
+            f.y = (nb > 0 && l_row > 0.f) ? __uint_as_float(o[4 * v + 1]) : 0.f;
+            f.z = (nb > 0 && l_row > 0.f) ? __uint_as_float(o[4 * v + 2]) : 0.f;
+            f.w = (nb > 0 && l_row > 0.f) ? __uint_as_float(o[4 * v + 3]) : 0.f;
+            *reinterpret_cast<float4*>(dst + c + 4 * v) = f;
+          }
+        }
+        if (lane < 16) {
+          p.part_ml[slot * 2 + 0] = m_row;
+          p.part_ml[slot * 2 + 1] = l_row;
+        }
+      }
+    }
+  }
+
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    sm100::tc_fence_after_sync();
+    sm100::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Merge of the per-split partials: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s.
+__global__ void __launch_bounds__(128)
+mla_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                   const float* __restrict__ part_ml, int Hh, int nsplit) {
+  const int bh = blockIdx.x;                // b * Hh + h
+  const int b = bh / Hh, h = bh - b * Hh;
+  float m = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[(((size_t)b * nsplit + s) * Hh + h) * 2]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const size_t slot = ((size_t)b * nsplit + s) * Hh + h;
+    const float ms = part_ml[slot * 2], ls = part_ml[slot * 2 + 1];
+    if (ls <= 0.f || ms == -INFINITY) continue;
+    const float w = exp2f(ms - m);
+    const float4 o = *reinterpret_cast<const float4*>(part_o + slot * kDv + threadIdx.x * 4);
+    acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+    l += w * ls;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  uint2 w2;
+  w2.x = *reinterpret_cast<uint32_t*>(&lo);
+  w2.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(out + (size_t)bh * kDv + threadIdx.x * 4) = w2;
+}
+
+// Index validation + row gather on its own: rows[b, j, :] = kv[b, idx[b, j], :] or zeros.
+__global__ void __launch_bounds__(256)
+mla_gather_rows_kernel(uint4* __restrict__ rows, const uint4* __restrict__ kv, const int* __restrict__ seq_len,
+                       const int* __restrict__ idx, int S, int topk, long long total) {
+  const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte piece each
+  if (id >= total) return;
+  const int piece = (int)(id % 72);
+  const long long rowid = id / 72;
+  const int b = (int)(rowid / topk);
+  const int t = __ldg(idx + rowid);
+  const bool ok = t >= 0 && t < __ldg(seq_len + b);
+  rows[id] = ok ? __ldg(kv + ((size_t)b * S + t) * 72 + piece) : make_uint4(0, 0, 0, 0);
+}
+
+}  // namespace
+
+extern "C" size_t mla_sparse_decode_scratch_bytes(int B, int Hh, int nsplit) {
+  if (nsplit <= 1) return 0;
+  return (size_t)B * nsplit * Hh * (kDv + 2) * sizeof(float);
+}
+
+extern "C" int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv,
+                                          const int* seq_len, const int* idx, int B, int Hh, int S, int topk,
+                                          float softmax_scale, int nsplit, void* scratch, int* status, int config,
+                                          cudaStream_t stream) {
+  (void)config;
+  if (B == 0) return CAB_OK;
+  if (!out || !q || !kv || !seq_len || !idx) return CAB_ERR_BAD_ARGUMENT;
+  if (B < 0 || Hh <= 0 || Hh % kHeads != 0 || S <= 0 || topk <= 0 || nsplit <= 0) return CAB_ERR_BAD_ARGUMENT;
+  if (nsplit > 1 && !scratch) return CAB_ERR_BAD_ARGUMENT;
+  if (B > 65535 || nsplit > 65535) return CAB_ERR_TOO_LARGE;
+  if (!cab::aligned_to(out, 16) || !cab::aligned_to(q, 16) || !cab::aligned_to(kv, 16) ||
+      (scratch && !cab::aligned_to(scratch, 16)))
+    return CAB_ERR_MISALIGNED;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(mla_sparse_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+        cudaSuccess)
+      return CAB_ERR_LAUNCH;
+    configured = true;
+  }
+  MlaParams p;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);
+  p.seq_len = seq_len; p.idx = idx;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.part_o = static_cast<float*>(scratch);
+  p.part_ml = p.part_o ? p.part_o + (size_t)B * nsplit * Hh * kDv : nullptr;
+  p.Hh = Hh; p.S = S; p.topk = topk; p.nsplit = nsplit;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  if (status && cudaMemsetAsync(status, 0, sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
+  mla_sparse_decode_kernel<<<dim3(Hh / kHeads, nsplit, B), kThreads, kSmemBytes, stream>>>(p);
+  int rc = cab::launch_status();
+  if (rc != CAB_OK || nsplit == 1) return rc;
+  mla_combine_kernel<<<B * Hh, 128, 0, stream>>>(p.out, p.part_o, p.part_ml, Hh, nsplit);
+  return cab::launch_status();
+}
+
+extern "C" int mla_gather_rows_launcher(cab_bf16* rows, const cab_bf16* kv, const int* seq_len, const int* idx,
+                                        int B, int S, int topk, int config, cudaStream_t stream) {
+  (void)config;
+  if (B == 0 || topk == 0) return CAB_OK;
+  if (!rows || !kv || !seq_len || !idx || B < 0 || S <= 0 || topk < 0) return CAB_ERR_BAD_ARGUMENT;
+  if (!cab::aligned_to(rows, 16) || !cab::aligned_to(kv, 16)) return CAB_ERR_MISALIGNED;
+  const long long total = (long long)B * topk * 72;
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return CAB_ERR_TOO_LARGE;
+  mla_gather_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<uint4*>(rows),
+                                                               reinterpret_cast<const uint4*>(kv), seq_len, idx, S,
+                                                               topk, total);
+  return cab::launch_status();
+}

@@ -66,6 +66,42 @@ class MoeWorkload:
                                     False, config)
 
 
+class MlaWorkload:
+    """Top-k sparse MLA decode: B sequences, 128 heads, 2048 of up to 32768 cached rows each."""
+
+    def __init__(self, dev, B=64, Hh=128, S=32768, topk=2048, min_len=8192, seed=1236):
+        self.B, self.Hh, self.S, self.topk, self.dev = B, Hh, S, topk, dev
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        self.q = torch.randn(B, 1, Hh, 576, device=dev, generator=gen).to(torch.bfloat16)
+        self.kv = torch.empty(B, S, 576, dtype=torch.bfloat16, device=dev)
+        for b in range(B):
+            self.kv[b] = torch.randn(S, 576, device=dev, generator=gen).to(torch.bfloat16)
+        self.seq_len = torch.randint(min_len, S + 1, (B,), device=dev, generator=gen, dtype=torch.int32)
+        idx = torch.full((B, 1, topk), -1, dtype=torch.int32, device=dev)
+        for b in range(B):
+            n = int(self.seq_len[b])
+            chosen = torch.randperm(n, device=dev, generator=gen)[:topk].to(torch.int32)
+            idx[b, 0, : chosen.numel()] = chosen
+        self.idx = idx
+        self.out = torch.empty(B, 1, Hh, 512, dtype=torch.bfloat16, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.scale = 192 ** -0.5
+        self.ext = load_extension()
+        self.bytes = B * topk * 576 * 2 + self.q.numel() * 2 + self.out.numel() * 2 + idx.numel() * 4
+        self.flops = 2 * B * Hh * topk * (576 + 512)
+        self.scratch = {}
+
+    def step(self, nsplit=1, config=0):
+        if nsplit not in self.scratch:
+            n = capi.mla_scratch_bytes(self.B, self.Hh, nsplit)
+            self.scratch[nsplit] = torch.empty(max(n, 16), dtype=torch.uint8, device=self.dev) if n else None
+        capi.mla_sparse_decode(self.out, self.q, self.kv, self.seq_len, self.idx, self.scale, nsplit,
+                               self.scratch[nsplit], self.status, config)
+
+    def api_step(self, q, idx, seq_len):
+        return self.ext.mla_sparse_decode_forward(q, self.kv, seq_len, idx, self.scale, 0, False, 0)
+
+
 def time_cuda(fn, steps: int, warmup: int) -> float:
     """Milliseconds per call between two CUDA events on the current stream."""
     for _ in range(warmup):

@@ -27,6 +27,9 @@ SIGNATURES = {
     "moe_permute_launcher": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p]),
     "moe_quant_dispatch_launcher": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
     "moe_combine_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),
+    "mla_sparse_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "mla_sparse_decode_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "mla_gather_rows_launcher": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p]),
     "moe_grouped_gemm_fp8_launcher": (c_int, [c_int] + [c_void_p] * 8 + [c_int] * 6 + [c_void_p, c_int, c_void_p]),
 }
 
@@ -164,3 +167,24 @@ def moe_grouped_gemm_fp8(mode, out, out_scales_t, a_q, a_scales_t, w_q, w_scales
                                                _p(w_q), _p(w_scales), _opt(tile_expert), _opt(num_tiles),
                                                max_m_tiles, rows_cap, a_scales_t.shape[1], E, N, K,
                                                _opt(status), config, _stream()))
+
+
+# ----------------------------------------------------------------------------- sparse MLA decode
+def mla_sparse_decode(out, q, kv, seq_len, idx, softmax_scale: float, nsplit: int = 1, scratch=None, status=None,
+                      config: int = 0) -> None:
+    B, _, Hh, _ = q.shape
+    S, topk = kv.shape[1], idx.shape[-1]
+    _check("mla_sparse_decode_launcher",
+           lib().mla_sparse_decode_launcher(_p(out), _p(q), _p(kv), _p(seq_len), _p(idx), B, Hh, S, topk,
+                                            softmax_scale, nsplit, _opt(scratch), _opt(status), config, _stream()))
+
+
+def mla_scratch_bytes(B: int, Hh: int, nsplit: int) -> int:
+    return lib().mla_sparse_decode_scratch_bytes(B, Hh, nsplit)
+
+
+def mla_gather_rows(rows, kv, seq_len, idx, config: int = 0) -> None:
+    B, S, _ = kv.shape
+    _check("mla_gather_rows_launcher",
+           lib().mla_gather_rows_launcher(_p(rows), _p(kv), _p(seq_len), _p(idx), B, S, idx.shape[-1], config,
+                                          _stream()))

@@ -178,6 +178,33 @@ int moe_grouped_gemm_fp8_launcher(int mode, void* out, float* out_scales_t, cons
                                   int rows_cap, int ld_rows, int E, int N, int K, int* status,
                                   int config, cab_stream_t stream);
 
+/* ------------------------------------------------------------------------- */
+/* Top-k sparse MLA decode attention (absorbed latent attention, one query      */
+/* token per sequence). The reference ships no such op; these launchers fill     */
+/* the kernel slot of agent_workdir/kernels/ (ABI of axpby.cu:12-20).            */
+/*   q        bf16 [B, 1, Hh, 576]   (512 latent + 64 rope dims), Hh % 64 == 0   */
+/*   kv       bf16 [B, S, 576]       latent KV cache                             */
+/*   seq_len  int32 [B]              valid rows per sequence                     */
+/*   idx      int32 [B, 1, topk]     selected rows, shared by all heads; an      */
+/*                                   entry counts iff 0 <= idx < seq_len[b]      */
+/*   out      bf16 [B, 1, Hh, 512] = softmax(q . kv[idx]^T * softmax_scale)      */
+/*                                   . kv[idx][:, :512]; zeros if nothing valid  */
+/* nsplit > 1 divides the topk entries over nsplit CTAs per (sequence, 64 heads) */
+/* and merges their partial results; it needs `scratch`, device memory of        */
+/* mla_sparse_decode_scratch_bytes(B, Hh, nsplit) bytes (16-byte aligned,         */
+/* contents irrelevant on entry). status: as for moe_grouped_gemm_fp8_launcher.   */
+/* ------------------------------------------------------------------------- */
+size_t mla_sparse_decode_scratch_bytes(int B, int Hh, int nsplit);
+int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv, const int* seq_len,
+                               const int* idx, int B, int Hh, int S, int topk, float softmax_scale,
+                               int nsplit, void* scratch, int* status, int config, cab_stream_t stream);
+
+/* The index-validation + row-gather step on its own:                            */
+/* rows[b, j, :] (bf16 [B, topk, 576]) = kv[b, idx[b, j], :] for a valid entry,   */
+/* zeros otherwise.                                                              */
+int mla_gather_rows_launcher(cab_bf16* rows, const cab_bf16* kv, const int* seq_len, const int* idx, int B,
+                             int S, int topk, int config, cab_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

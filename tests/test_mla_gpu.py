@@ -1,0 +1,102 @@
+"""GPU parity of sparse MLA decode against the eager oracle, through the C ABI and the extension.
+
+Tolerance (stated for this path): atol 2e-2 on the bf16 output; the row gather is bit-exact.
+"""
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT, load_oracle
+
+pytestmark = pytest.mark.gpu
+ATOL = 2e-2
+
+
+def run(dev, q, kv, seq_len, idx, nsplit):
+    from cuda_agent_b200 import capi
+    B, _, Hh, _ = q.shape
+    out = torch.full((B, 1, Hh, 512), float("nan"), dtype=torch.bfloat16, device=dev)
+    status = torch.ones(1, dtype=torch.int32, device=dev)
+    nbytes = capi.mla_scratch_bytes(B, Hh, nsplit)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev) if nbytes else None
+    capi.mla_sparse_decode(out, q.to(dev), kv.to(dev), seq_len.to(dev), idx.to(dev), 192 ** -0.5, nsplit, scratch,
+                           status)
+    torch.cuda.synchronize()
+    assert int(status) == 0, f"bounded wait gave up at code {int(status)}"
+    return out.cpu()
+
+
+@pytest.mark.parametrize("nsplit", [1, 2, 3])
+@pytest.mark.parametrize("B,Hh,S,topk,min_len", [(1, 64, 128, 64, 100), (2, 64, 300, 128, 40), (3, 128, 500, 200, 20),
+                                                 (2, 128, 4096, 2048, 1500)])
+def test_matches_oracle(cuda_device, B, Hh, S, topk, min_len, nsplit):
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    gen = torch.Generator().manual_seed(B * 100 + topk)
+    q, kv, seq_len, idx = m.make_inputs(B, Hh, S, topk, min_len, gen)
+    idx[0, 0, 3] = -1
+    idx[B - 1, 0, topk // 2] = S + 5
+    ref = m.Model(B, Hh, S, topk)(q, kv, seq_len, idx)
+    out = run(cuda_device, q, kv, seq_len, idx, nsplit)
+    assert torch.isfinite(out.float()).all()
+    err = float((out.float() - ref.float()).abs().max())
+    assert err <= ATOL, err
+
+
+def test_edge_cases(cuda_device):
+    """Nothing valid -> zeros; a single valid entry -> that row; wide score range (lazy rescale path)."""
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    gen = torch.Generator().manual_seed(9)
+    q, kv, seq_len, idx = m.make_inputs(3, 64, 400, 192, 300, gen)
+    idx[0] = -1                                     # sequence 0: nothing selected
+    idx[1] = -1; idx[1, 0, 77] = 5                  # sequence 1: exactly one row
+    q[2] = q[2] * 6                                 # sequence 2: scores spread over > 2^8, late maxima
+    kv[2, :, :] = kv[2, :, :] * torch.linspace(0.2, 3.0, 400)[:, None].to(torch.bfloat16)
+    ref = m.Model(3, 64, 400, 192)(q, kv, seq_len, idx)
+    for nsplit in (1, 3):
+        out = run(cuda_device, q, kv, seq_len, idx, nsplit)
+        assert torch.all(out[0] == 0)
+        torch.testing.assert_close(out[1, 0].float(), kv[1, 5, :512].float().expand(64, 512), rtol=0, atol=1e-2)
+        assert float((out[2].float() - ref[2].float()).abs().max()) <= 6e-2     # |values| up to ~10 here
+
+
+def test_gather_rows_exact(cuda_device):
+    from cuda_agent_b200 import capi
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    gen = torch.Generator().manual_seed(4)
+    q, kv, seq_len, idx = m.make_inputs(3, 64, 700, 256, 100, gen)
+    idx[0, 0, :7] = torch.tensor([-1, 10 ** 6, 0, 699, int(seq_len[0]), int(seq_len[0]) - 1, -5])
+    rows = torch.full((3, 256, 576), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    capi.mla_gather_rows(rows, kv.to(cuda_device), seq_len.to(cuda_device), idx.to(cuda_device))
+    assert torch.equal(rows.cpu().view(torch.int16), m.gather_rows(kv, idx, seq_len).view(torch.int16))
+
+
+def test_extension_and_verification_loop(cuda_device, built_libs, capsys):
+    import os
+    os.environ["CAB_MLA_CONFIG"] = "0"
+    sys.path.insert(0, str(built_libs.WORKDIR))
+    from utils import verification
+    # config 0 has 16 heads; the op needs a multiple of 64, so the loop runs a 64-head variant
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    import cuda_agent_b200
+    ext = cuda_agent_b200.load_extension()
+    gen = torch.Generator().manual_seed(2)
+    q, kv, seq_len, idx = m.make_inputs(4, 64, 600, 320, 200, gen)
+    ref = m.Model(4, 64, 600, 320)(q, kv, seq_len, idx)
+    out = ext.mla_sparse_decode_forward(q.to(cuda_device), kv.to(cuda_device), seq_len.to(cuda_device),
+                                        idx.to(cuda_device), 192 ** -0.5, 0, True, 0)
+    assert float((out.cpu().float() - ref.float()).abs().max()) <= ATOL
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        ext.mla_sparse_decode_forward(q[:, :, :16].contiguous().to(cuda_device), kv.to(cuda_device),
+                                      seq_len.to(cuda_device), idx.to(cuda_device), 0.07, 0, False, 0)
+
+
+def test_config2_sampled_batches(cuda_device):
+    """Full-size shapes (128 heads, 2048 of up to 32768 rows) on 4 sequences against the oracle."""
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 2})
+    gen = torch.Generator().manual_seed(1236)
+    q, kv, seq_len, idx = m.make_inputs(4, 128, 32768, 2048, 8192, gen)
+    ref = m.Model(4, 128, 32768, 2048)(q, kv, seq_len, idx)
+    for nsplit in (1, 4):
+        out = run(cuda_device, q, kv, seq_len, idx, nsplit)
+        assert float((out.float() - ref.float()).abs().max()) <= ATOL
