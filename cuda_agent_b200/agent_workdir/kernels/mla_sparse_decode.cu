@@ -151,31 +151,40 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
     const int ptid = threadIdx.x - 5 * 32;
     const int* idx_b = p.idx + (size_t)b * p.topk;
     const __nv_bfloat16* kv_b = p.kv + (size_t)b * p.S * kDqk;
-    for (int j = 0; j < nb + 1; ++j) {
-      if (j < nb) {
-        const int st = j & 1;
-        if (j >= 2 && !sm100::mbar_wait_relaxed(&ctl.kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kWaitKvEmpty))
-          break;
-        const int tok0 = (j0 + j) * kTok;
-        if (ptid < kTok) {
-          const int i = tok0 + ptid;
-          const int t = i < p.topk ? __ldg(idx_b + i) : -1;
-          ctl.valid[st][ptid] = (t >= 0 && t < len) ? 1 : 0;
-        }
-        gather_tile(sm100::smem_u32(kv_tile + st * kTileBytes), ptid, kProducerThreads, [&](int r) {
-          const int i = tok0 + r;
-          const int t = i < p.topk ? __ldg(idx_b + i) : -1;
-          // an invalid entry copies row 0: finite data that the mask multiplies by zero
-          return kv_b + (size_t)((t >= 0 && t < len) ? t : 0) * kDqk;
-        });
-      }
-      cp_async_commit();
+    // Iteration j: publish block j-1 as soon as it has landed (nothing newer is in flight yet), then
+    // wait for the stage of block j to be released by P.V of block j-2 and start its copies. Block j is
+    // in flight while block j-1 is computed.
+    for (int j = 0; j <= nb; ++j) {
       if (j >= 1) {
-        // block j-1 has landed: make it visible to the tensor core and publish it
-        cp_async_wait<1>();
+        cp_async_wait<0>();
         sm100::fence_proxy_async();
         sm100::mbar_arrive(&ctl.kv_full[(j - 1) & 1]);
       }
+      if (j == nb) break;
+      const int st = j & 1;
+      if (j >= 2 && !sm100::mbar_wait_relaxed(&ctl.kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kWaitKvEmpty))
+        break;
+      // Warp w of the producers owns rows 16w..16w+15 of the block: lane l fetches the cache row
+      // number of row 16w + (l & 15) once, the 1152 sixteen-byte pieces of the 16 rows are then
+      // spread over the lanes (36 each) and every piece learns its row by shuffle.
+      const int pw = ptid >> 5;
+      const int my_i = (j0 + j) * kTok + pw * 16 + (lane & 15);
+      const int my_t = my_i < p.topk ? __ldg(idx_b + my_i) : -1;
+      const bool my_ok = my_t >= 0 && my_t < len;
+      if (lane < 16) ctl.valid[st][pw * 16 + lane] = my_ok ? 1 : 0;
+      // an invalid entry copies row 0: finite data that the mask multiplies by zero
+      const int my_row = my_ok ? my_t : 0;
+      const uint32_t dst = sm100::smem_u32(kv_tile + st * kTileBytes);
+#pragma unroll 4
+      for (int it = 0; it < 36; ++it) {
+        const int piece = it * 32 + lane;
+        const int rl = piece / 72, c16 = piece - rl * 72;
+        const int t = __shfl_sync(0xffffffffu, my_row, rl);
+        const int r = pw * 16 + rl;
+        cp_async_16(dst + (c16 >> 3) * kChunkBytes + r * 128 + (((c16 & 7) ^ (r & 7)) << 4),
+                    kv_b + (size_t)t * kDqk + c16 * 8);
+      }
+      cp_async_commit();
     }
   } else if (warp == 4) {
     // ---------------------------------------------------------------- MMA issuer
@@ -246,12 +255,16 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl.s_empty[st]);
 
+      // validity of the block's 64 entries as two ballots
+      const unsigned v_lo = __ballot_sync(0xffffffffu, ctl.valid[st][lane] != 0);
+      const unsigned v_hi = __ballot_sync(0xffffffffu, ctl.valid[st][lane + 32] != 0);
       float s[kTok];
       float m_blk = -INFINITY;
 #pragma unroll
       for (int i = 0; i < kTok; ++i) {
         const float raw = __uint_as_float(i < 32 ? t0[i] : t1[i - 32]);
-        s[i] = (row_ok && ctl.valid[st][i]) ? raw * p.scale_log2 : -INFINITY;
+        const bool live = row_ok && (((i < 32 ? v_lo : v_hi) >> (i & 31)) & 1u);
+        s[i] = live ? raw * p.scale_log2 : -INFINITY;
         m_blk = fmaxf(m_blk, s[i]);
       }
       // lazy reference maximum: move it only on the first non-empty block or on a jump > 2^8
@@ -264,12 +277,12 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
           m_ref = m_blk;
         }
       }
+      const float m_sub = m_ref == -INFINITY ? 0.f : m_ref;   // exp2(-inf - m_sub) = 0 for masked entries
       float psum = 0.f;
       uint32_t packed[kTok / 2];
 #pragma unroll
       for (int i = 0; i < kTok; i += 2) {
-        const float p0 = s[i] == -INFINITY ? 0.f : exp2f(s[i] - m_ref);
-        const float p1 = s[i + 1] == -INFINITY ? 0.f : exp2f(s[i + 1] - m_ref);
+        const float p0 = exp2f(s[i] - m_sub), p1 = exp2f(s[i + 1] - m_sub);
         psum += p0 + p1;
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
