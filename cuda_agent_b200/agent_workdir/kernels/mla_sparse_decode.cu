@@ -22,6 +22,8 @@
 #include "cab_common.cuh"
 #include "sm100_primitives.cuh"
 
+#include <mutex>
+
 namespace {
 
 constexpr int kDqk = 576, kDv = 512;
@@ -487,4 +489,63 @@ extern "C" int mla_gather_rows_launcher(cab_bf16* rows, const cab_bf16* kv, cons
                                                                reinterpret_cast<const uint4*>(kv), seq_len, idx, S,
                                                                topk, total);
   return cab::launch_status();
+}
+
+namespace {
+// ------------------------------------------------------------------------------------------------
+// Split decode without any allocation.
+//
+// Some hosts of this library cannot give the split-KV path its scratch buffer: a serving process
+// that handed all device memory to its own arena at start-up and forbids cudaMalloc on the request
+// path (an allocation may fail there, and it synchronises the device), or a plugin interface whose
+// operator signature carries inputs and outputs only, with no workspace argument and no allocator
+// to call. For them the partial results live in a fixed array inside this library's device image.
+//
+// The array costs kStaticScratchBytes of device memory on every GPU that loads the library, from
+// load until the process exits, whether or not this entry point is ever called. It is shared by all
+// calls on that GPU: two calls whose kernels can overlap on the device (different streams, or
+// different host threads) race on it and must be serialised by the caller. It keeps whatever the
+// last call left in it; nothing has to be cleared, because every slot the merge kernel reads was
+// written by the decode kernel of the same call.
+constexpr size_t kStaticScratchBytes = CAB_MLA_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_mla_static_scratch[kStaticScratchBytes];
+
+// In host code `g_mla_static_scratch` is only a handle for the runtime, not a device address; the
+// address has to be asked for, once per device, with that device current.
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {};
+std::mutex g_scratch_mutex;
+
+int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return CAB_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_addr[dev]) {
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_mla_static_scratch) != cudaSuccess || !addr) return CAB_ERR_LAUNCH;
+    g_scratch_addr[dev] = addr;
+  }
+  *out = g_scratch_addr[dev];
+  return CAB_OK;
+}
+
+}  // namespace
+
+extern "C" int mla_sparse_decode_noalloc_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv,
+                                                  const int* seq_len, const int* idx, int B, int Hh, int S,
+                                                  int topk, float softmax_scale, int nsplit, int* status,
+                                                  int config, cudaStream_t stream) {
+  if (B == 0) return CAB_OK;
+  if (B < 0 || Hh <= 0 || nsplit <= 0) return CAB_ERR_BAD_ARGUMENT;
+  // (B * nsplit * Hh) slots of 512 + 2 floats must fit the fixed array
+  const unsigned long long need = (unsigned long long)B * (unsigned long long)nsplit * (unsigned long long)Hh *
+                                  (kDv + 2) * sizeof(float);
+  if (nsplit > 1 && need > kStaticScratchBytes) return CAB_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  if (nsplit > 1) {
+    const int rc = static_scratch_address(&scratch);   // first call on a device looks the address up
+    if (rc != CAB_OK) return rc;
+  }
+  return mla_sparse_decode_launcher(out, q, kv, seq_len, idx, B, Hh, S, topk, softmax_scale, nsplit, scratch,
+                                    status, config, stream);
 }

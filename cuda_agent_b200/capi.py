@@ -29,6 +29,7 @@ SIGNATURES = {
     "moe_combine_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),
     "mla_sparse_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mla_sparse_decode_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "mla_sparse_decode_noalloc_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p, c_int, c_void_p]),
     "mla_gather_rows_launcher": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p]),
     "moe_grouped_gemm_fp8_launcher": (c_int, [c_int] + [c_void_p] * 8 + [c_int] * 6 + [c_void_p, c_int, c_void_p]),
 }
@@ -188,3 +189,20 @@ def mla_gather_rows(rows, kv, seq_len, idx, config: int = 0) -> None:
     _check("mla_gather_rows_launcher",
            lib().mla_gather_rows_launcher(_p(rows), _p(kv), _p(seq_len), _p(idx), B, S, idx.shape[-1], config,
                                           _stream()))
+
+
+MLA_STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
+
+
+def mla_sparse_decode_noalloc(out, q, kv, seq_len, idx, softmax_scale: float, nsplit: int, status=None,
+                              config: int = 0) -> None:
+    """Split decode whose partials live in the library's fixed device array: nothing is allocated.
+
+    For hosts that cannot hand over scratch memory (their allocator is closed while serving, or their
+    operator interface has no workspace argument). Raises CabError(status 4) when
+    B * nsplit * Hh * 2056 bytes exceed MLA_STATIC_SCRATCH_BYTES. Calls on one GPU share the array."""
+    B, _, Hh, _ = q.shape
+    S, topk = kv.shape[1], idx.shape[-1]
+    _check("mla_sparse_decode_noalloc_launcher",
+           lib().mla_sparse_decode_noalloc_launcher(_p(out), _p(q), _p(kv), _p(seq_len), _p(idx), B, Hh, S, topk,
+                                                    softmax_scale, nsplit, _opt(status), config, _stream()))

@@ -199,6 +199,28 @@ int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16*
                                const int* idx, int B, int Hh, int S, int topk, float softmax_scale,
                                int nsplit, void* scratch, int* status, int config, cab_stream_t stream);
 
+/* Split decode that allocates nothing. No counterpart in the reference.          */
+/* Same arguments and result as mla_sparse_decode_launcher, without the scratch    */
+/* pointer: the split partials go to a fixed array of                               */
+/* CAB_MLA_STATIC_SCRATCH_BYTES inside the library's device image. It exists for    */
+/* callers that cannot provide scratch: a process whose device memory is already    */
+/* owned by its own arena and that must not call cudaMalloc while serving, or an    */
+/* operator interface that passes inputs and outputs only.                          */
+/*  - B * nsplit * Hh * 2056 bytes must not exceed CAB_MLA_STATIC_SCRATCH_BYTES;      */
+/*    otherwise CAB_ERR_TOO_LARGE is returned and nothing is launched.               */
+/*  - The array occupies that much memory on every GPU that loads the library,      */
+/*    until the process exits.                                                       */
+/*  - All calls on a GPU share it: calls that can overlap on the device race and     */
+/*    must be serialised by the caller. Old contents never leak into a result.       */
+/*  - The first call on each device looks up the array's device address (a host      */
+/*    call to the CUDA runtime); make that first call before capturing any stream.   */
+/*  - It calls no cudaMalloc, cudaFree or other allocating routine.                   */
+#define CAB_MLA_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+int mla_sparse_decode_noalloc_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv,
+                                       const int* seq_len, const int* idx, int B, int Hh, int S, int topk,
+                                       float softmax_scale, int nsplit, int* status, int config,
+                                       cab_stream_t stream);
+
 /* The index-validation + row-gather step on its own:                            */
 /* rows[b, j, :] (bf16 [B, topk, 576]) = kv[b, idx[b, j], :] for a valid entry,   */
 /* zeros otherwise.                                                              */
