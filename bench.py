@@ -60,7 +60,7 @@ def parse_args():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--config", type=int, default=0, help="launcher variant passed to the op")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["gdn", "moe", "mla"], default="gdn",
+    ap.add_argument("--workload", choices=["gdn", "moe", "mla", "moe_ep"], default="gdn",
                     help="gdn = the headline line; moe = FP8 MoE layer (4096 tokens, 64 experts, top-6); "
                          "mla = top-2048 sparse MLA decode (64 sequences, 128 heads)")
     ap.add_argument("--nsplit", type=int, default=1, help="mla: splits of the selected rows per CTA group")
@@ -475,8 +475,90 @@ def run_mla(args):
     print(json.dumps(line), flush=True)
 
 
+def run_moe_ep(args):
+    """Secondary line: the expert-parallel FP8 MoE layer (8192 tokens per GPU, H 7168, I 2048, 256 experts
+    over the ranks, top-8 group-limited sigmoid routing, one shared expert). Launch with torchrun for N > 1.
+    value = GEMM FLOP of all ranks / max-over-ranks layer time (CUDA events around the whole layer call,
+    all-to-all exchanges included). e2e adds the host round trip of x and the output."""
+    import torch
+    import torch.distributed as dist
+    from cuda_agent_b200.benchmarks import MoeEpWorkload
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    wl = MoeEpWorkload(dev, rank, world)
+    steps, warmup = min(args.steps, 30), max(3, min(args.warmup, 5))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    w0 = time.monotonic()
+    ms = timed(wl.step)
+    hx = wl.x.cpu().pin_memory()
+    ho = torch.empty_like(hx).pin_memory()
+    dx = torch.empty_like(wl.x)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        ho.copy_(wl.step(dx), non_blocking=True)
+    ms_e2e = timed(e2e_step)
+    windows = [(w0, time.monotonic())]
+    sampler.stop()
+    assert wl.ops.status.cpu().tolist() == [0, 0, 0, 0]
+    if rank == 0:
+        tflops = wl.flops_per_gpu * world / (ms * 1e-3) / 1e12
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        peak = 2.0 * (float(json.loads(peaks_file.read_text())["bf16_tflops"]) if peaks_file.exists() else 1590.0)
+        line = {
+            "metric": "moe_ep_fp8_layer_tflops", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+            "config": {"workload": "moe_ep_layer", "T_per_gpu": wl.T, "H": wl.H, "I": wl.I, "E": wl.E, "k": wl.k,
+                       "experts_per_gpu": wl.E // world, "shared_experts": 1, "flops_per_gpu": wl.flops_per_gpu,
+                       "parallelism": f"ep{world}, NCCL all-to-all dispatch/return",
+                       "l2": "expert weights (>= 1.4 GB per GPU) exceed L2; no flush needed"},
+            "e2e": {"value": round(wl.flops_per_gpu * world / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": hx.numel() * 2 * world, "d2h_bytes_per_step": ho.numel() * 2 * world,
+                    "ms_per_step": round(ms_e2e, 4), "api": "cuda_agent_b200.ep.ep_moe_forward"},
+            "gpu_launches": steps * 14,
+            "roofline": {"bound": "tensor", "kernel": "moe_gemm_fp8_kernel (layer time incl. exchanges)",
+                         "achieved": round(tflops / world, 2), "peak": peak, "unit": "TFLOP/s",
+                         "frac": round(tflops / world / peak, 4), "traffic": None,
+                         "peak_source": "2 x measured bf16 burst; per GPU"},
+            "clocks": sampler.summary(windows),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
+    if args.workload == "moe_ep" and args.impl != "reference":
+        return run_moe_ep(args)
     if args.workload == "moe" and args.impl != "reference":
         return run_moe(args)
     if args.workload == "mla" and args.impl != "reference":

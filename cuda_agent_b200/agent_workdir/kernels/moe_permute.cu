@@ -142,6 +142,8 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 // (16 bytes); a 128-column quantisation block is a half-warp. The quantised row
 // is written to every destination row of the token (k of them, or row t itself
 // when dst_row is null), scales go to the transposed table sc_t[block][row].
+// ROW_MAJOR_SCALES: scales go to sc[row * (H/128) + block] instead (the layout a row travels in).
+template <bool ROW_MAJOR_SCALES>
 __global__ void __launch_bounds__(256)
 moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int k,
                           const int* __restrict__ dst_row, uint8_t* __restrict__ a_q,
@@ -173,7 +175,10 @@ moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int
       const int row = dst_row ? __shfl_sync(0xffffffffu, my_dst, s) : t;
       if (live && row >= 0) {
         *reinterpret_cast<uint2*>(a_q + (size_t)row * H + col) = q;
-        if ((lane & 15) == 0) sc_t[(size_t)(col >> 7) * ld_rows + row] = scale;
+        if ((lane & 15) == 0) {
+          if (ROW_MAJOR_SCALES) sc_t[(size_t)row * (H >> 7) + (col >> 7)] = scale;
+          else sc_t[(size_t)(col >> 7) * ld_rows + row] = scale;
+        }
       }
     }
   }
@@ -218,6 +223,52 @@ moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
     *reinterpret_cast<uint4*>(out + (size_t)t * H + col) = o;
   }
+}
+
+// ------------------------------------------------------------------ expert-parallel row movement
+// Received rows (quantised bytes + row-major scales, in arrival order) -> the padded row space of the
+// local grouped GEMMs: a_q[dst_row[i]] = rows[i], scales transposed on the way.
+__global__ void __launch_bounds__(256)
+moe_scatter_rows_kernel(uint8_t* __restrict__ a_q, float* __restrict__ sc_t, const uint8_t* __restrict__ rows,
+                        const float* __restrict__ scales, const int* __restrict__ dst_row, int n, int H, int ld_rows) {
+  const int i = blockIdx.x;
+  const int d = __ldg(dst_row + i);
+  if (d < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(rows + (size_t)i * H);
+  uint4* dst = reinterpret_cast<uint4*>(a_q + (size_t)d * H);
+  for (int c = threadIdx.x; c < H / 16; c += blockDim.x) dst[c] = __ldcs(src + c);
+  for (int b = threadIdx.x; b < H / 128; b += blockDim.x) sc_t[(size_t)b * ld_rows + d] = __ldg(scales + (size_t)i * (H / 128) + b);
+}
+
+// out[i, :] = y[src_row[i], :] (bf16 rows of H elements): the way back, before the return exchange.
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ y, const int* __restrict__ src_row, int H) {
+  const int i = blockIdx.x;
+  const int s = __ldg(src_row + i);
+  const int n16 = H / 8;
+  for (int c = threadIdx.x; c < n16; c += blockDim.x)
+    out[(size_t)i * n16 + c] = s >= 0 ? __ldcs(y + (size_t)s * n16 + c) : make_uint4(0, 0, 0, 0);
+}
+
+// Tile table of the local experts from their populations (what moe_count_scan_kernel derives from
+// the routing when everything is local).
+__global__ void moe_tiles_from_counts_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets,
+                                             int* __restrict__ pad_offsets, int* __restrict__ tile_expert,
+                                             int* __restrict__ num_tiles, int max_tiles) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int off = 0, pad = 0, tiles = 0;
+  for (int e = 0; e < E; ++e) {
+    const int c = counts[e];
+    offsets[e] = off;
+    pad_offsets[e] = pad;
+    const int nt = (c + kTileM - 1) / kTileM;
+    for (int j = 0; j < nt && tiles + j < max_tiles; ++j) tile_expert[tiles + j] = e;
+    off += c; pad += nt * kTileM; tiles += nt;
+  }
+  offsets[E] = off;
+  pad_offsets[E] = pad;
+  num_tiles[0] = min(tiles, max_tiles);
+  for (int j = min(tiles, max_tiles); j < max_tiles; ++j) tile_expert[j] = -1;
 }
 
 }  // namespace
@@ -267,8 +318,20 @@ extern "C" int moe_quant_dispatch_launcher(cab_e4m3* a_q, float* scales_t, const
   if (!a_q || !scales_t || !x) return CAB_ERR_BAD_ARGUMENT;
   if (T < 0 || H <= 0 || H % 128 != 0 || k <= 0 || k > 32 || ld_rows <= 0) return CAB_ERR_BAD_ARGUMENT;
   if (!cab::aligned_to(a_q, 16) || !cab::aligned_to(x, 16)) return CAB_ERR_MISALIGNED;
-  moe_quant_dispatch_kernel<<<(T + 7) / 8, 256, 0, stream>>>(
+  moe_quant_dispatch_kernel<false><<<(T + 7) / 8, 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), T, H, k, dst_row, a_q, scales_t, ld_rows);
+  return cab::launch_status();
+}
+
+extern "C" int moe_quant_rows_launcher(cab_e4m3* rows_q, float* scales, const cab_bf16* x, const int* dst_row,
+                                       int T, int H, int k, int config, cudaStream_t stream) {
+  (void)config;
+  if (T == 0) return CAB_OK;
+  if (!rows_q || !scales || !x) return CAB_ERR_BAD_ARGUMENT;
+  if (T < 0 || H <= 0 || H % 128 != 0 || k <= 0 || k > 32) return CAB_ERR_BAD_ARGUMENT;
+  if (!cab::aligned_to(rows_q, 16) || !cab::aligned_to(x, 16)) return CAB_ERR_MISALIGNED;
+  moe_quant_dispatch_kernel<true><<<(T + 7) / 8, 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), T, H, k, dst_row, rows_q, scales, 0);
   return cab::launch_status();
 }
 
@@ -284,5 +347,38 @@ extern "C" int moe_combine_launcher(cab_bf16* out, const cab_bf16* y, const int*
   moe_combine_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(out),
                                             reinterpret_cast<const __nv_bfloat16*>(y), dst_row, weights,
                                             reinterpret_cast<const __nv_bfloat16*>(extra), T, H, k);
+  return cab::launch_status();
+}
+
+extern "C" int moe_scatter_rows_launcher(cab_e4m3* a_q, float* scales_t, const cab_e4m3* rows, const float* scales,
+                                         const int* dst_row, int n, int H, int ld_rows, int config,
+                                         cudaStream_t stream) {
+  (void)config;
+  if (n == 0) return CAB_OK;
+  if (!a_q || !scales_t || !rows || !scales || !dst_row) return CAB_ERR_BAD_ARGUMENT;
+  if (n < 0 || H <= 0 || H % 128 != 0 || ld_rows <= 0) return CAB_ERR_BAD_ARGUMENT;
+  if (!cab::aligned_to(a_q, 16) || !cab::aligned_to(rows, 16)) return CAB_ERR_MISALIGNED;
+  moe_scatter_rows_kernel<<<n, 256, 0, stream>>>(a_q, scales_t, rows, scales, dst_row, n, H, ld_rows);
+  return cab::launch_status();
+}
+
+extern "C" int moe_gather_rows_launcher(cab_bf16* out, const cab_bf16* y, const int* src_row, int n, int H,
+                                        int config, cudaStream_t stream) {
+  (void)config;
+  if (n == 0) return CAB_OK;
+  if (!out || !y || !src_row || n < 0 || H <= 0 || H % 8 != 0) return CAB_ERR_BAD_ARGUMENT;
+  if (!cab::aligned_to(out, 16) || !cab::aligned_to(y, 16)) return CAB_ERR_MISALIGNED;
+  moe_gather_rows_kernel<<<n, 256, 0, stream>>>(reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(y),
+                                                src_row, H);
+  return cab::launch_status();
+}
+
+extern "C" int moe_tiles_from_counts_launcher(const int* counts, int E, int* offsets, int* pad_offsets,
+                                              int* tile_expert, int* num_tiles, int max_tiles, int config,
+                                              cudaStream_t stream) {
+  (void)config;
+  if (!counts || !offsets || !pad_offsets || !tile_expert || !num_tiles || E <= 0 || max_tiles <= 0)
+    return CAB_ERR_BAD_ARGUMENT;
+  moe_tiles_from_counts_kernel<<<1, 32, 0, stream>>>(counts, E, offsets, pad_offsets, tile_expert, num_tiles, max_tiles);
   return cab::launch_status();
 }

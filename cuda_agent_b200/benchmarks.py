@@ -66,6 +66,37 @@ class MoeWorkload:
                                     False, config)
 
 
+class MoeEpWorkload:
+    """DeepSeek-V3-shaped expert-parallel layer: T tokens per GPU, H 7168, I 2048, 256 routed experts in
+    blocks of 256/N per rank, top-8 sigmoid routing with 8 groups / top-4, one shared expert."""
+
+    def __init__(self, dev, rank, world, T=8192, H=7168, I=2048, E=256, k=8, seed=1238):
+        from .ep import CudaOps
+        self.T, self.H, self.I, self.E, self.k, self.world = T, H, I, E, k, world
+        gen = torch.Generator(device=dev).manual_seed(seed)           # same router on every rank
+        router_w = (torch.randn(E, H, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        router_bias = torch.randn(E, device=dev, generator=gen) * 0.02
+        gen_r = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
+        self.x = torch.randn(T, H, device=dev, generator=gen_r).to(torch.bfloat16)
+        el = E // world
+        w13_q = torch.empty(el, 2 * I, H, dtype=torch.float8_e4m3fn, device=dev)
+        w13_s = torch.empty(el, 2 * I // 128, H // 128, device=dev)
+        w2_q = torch.empty(el, H, I, dtype=torch.float8_e4m3fn, device=dev)
+        w2_s = torch.empty(el, H // 128, I // 128, device=dev)
+        for e in range(el):
+            w13_q[e], w13_s[e] = quant_128x128(torch.randn(2 * I, H, device=dev, generator=gen_r) * 0.02)
+            w2_q[e], w2_s[e] = quant_128x128(torch.randn(H, I, device=dev, generator=gen_r) * 0.02)
+        s13 = quant_128x128(torch.randn(2 * I, H, device=dev, generator=gen_r) * 0.02)
+        s2 = quant_128x128(torch.randn(H, I, device=dev, generator=gen_r) * 0.02)
+        self.ops = CudaOps(router_w, router_bias, w13_q, w13_s, w2_q, w2_s, (s13[0], s13[1], s2[0], s2[1]), k=k,
+                           routing=1, n_group=8, topk_group=4, scaling=1.0, num_experts=E)
+        self.flops_per_gpu = 6 * T * k * H * I + 6 * T * H * I          # routed + shared expert GEMMs
+
+    def step(self, x=None):
+        from .ep import ep_moe_forward
+        return ep_moe_forward(self.x if x is None else x, self.ops, self.world)
+
+
 class MlaWorkload:
     """Top-k sparse MLA decode: B sequences, 128 heads, 2048 of up to 32768 cached rows each."""
 

@@ -26,6 +26,10 @@ SIGNATURES = {
     "moe_permute_max_tiles": (c_int, [c_int, c_int, c_int]),
     "moe_permute_launcher": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p]),
     "moe_quant_dispatch_launcher": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
+    "moe_quant_rows_launcher": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p]),
+    "moe_scatter_rows_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),
+    "moe_gather_rows_launcher": (c_int, [c_void_p] * 3 + [c_int] * 3 + [c_void_p]),
+    "moe_tiles_from_counts_launcher": (c_int, [c_void_p, c_int] + [c_void_p] * 4 + [c_int, c_int, c_void_p]),
     "moe_combine_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),
     "mla_sparse_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mla_sparse_decode_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
@@ -206,3 +210,28 @@ def mla_sparse_decode_noalloc(out, q, kv, seq_len, idx, softmax_scale: float, ns
     _check("mla_sparse_decode_noalloc_launcher",
            lib().mla_sparse_decode_noalloc_launcher(_p(out), _p(q), _p(kv), _p(seq_len), _p(idx), B, Hh, S, topk,
                                                     softmax_scale, nsplit, _opt(status), config, _stream()))
+
+
+# ----------------------------------------------------------------------------- expert-parallel row movement
+def moe_quant_rows(rows_q, scales, x, dst_row, k: int) -> None:
+    T, H = x.shape
+    _check("moe_quant_rows_launcher",
+           lib().moe_quant_rows_launcher(_p(rows_q), _p(scales), _p(x), _opt(dst_row), T, H, k, 0, _stream()))
+
+
+def moe_scatter_rows(a_q, scales_t, rows, scales, dst_row) -> None:
+    n, H = rows.shape
+    _check("moe_scatter_rows_launcher",
+           lib().moe_scatter_rows_launcher(_p(a_q), _p(scales_t), _p(rows), _p(scales), _p(dst_row), n, H,
+                                           scales_t.shape[1], 0, _stream()))
+
+
+def moe_gather_rows(out, y, src_row) -> None:
+    n, H = out.shape
+    _check("moe_gather_rows_launcher", lib().moe_gather_rows_launcher(_p(out), _p(y), _p(src_row), n, H, 0, _stream()))
+
+
+def moe_tiles_from_counts(counts, offsets, pad_offsets, tile_expert, num_tiles) -> None:
+    _check("moe_tiles_from_counts_launcher",
+           lib().moe_tiles_from_counts_launcher(_p(counts), counts.numel(), _p(offsets), _p(pad_offsets),
+                                                _p(tile_expert), _p(num_tiles), tile_expert.numel(), 0, _stream()))

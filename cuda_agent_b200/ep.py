@@ -1,0 +1,200 @@
+"""Expert-parallel MoE layer: one process per GPU, experts in contiguous blocks of E/N per rank.
+
+Data path of one layer call on rank r (T local tokens, k experts per token):
+
+  route            logits, top-k -> idx [T,k] (global expert ids), weights [T,k]          (kernels)
+  permute          stable sort of the T*k entries by expert = by destination rank, then by
+                   that rank's local expert                                               (kernels)
+  quant_rows       1x128 e4m3 rows + row-major scales, written in sorted order            (kernel)
+  counts exchange  all-to-all of the [N, E/N] population matrix                           (NCCL)
+  dispatch         all-to-all of rows and scales with per-rank split sizes                (NCCL)
+  expert_ffn       scatter into the padded row space, grouped GEMM gate/up (+SwiGLU+
+                   re-quantise), grouped GEMM down, gather back into arrival order        (kernels)
+  return           all-to-all of the bf16 result rows, split sizes reversed               (NCCL)
+  combine          weighted sum per token in slot order (+ shared expert)                 (kernel)
+
+An entry travels once per (token, slot); merging the slots of one token that go to the same rank is a
+later step. The split sizes are needed on the host, so the counts exchange ends in one device-to-host
+copy per call.
+
+The bookkeeping (`ExchangePlan`) is integer tensor arithmetic that runs on any device; the compute is
+behind an `ops` object so that the same schedule runs over NCCL with the CUDA kernels (`CudaOps`) and,
+in the CPU tests, over gloo with a stand-in. `CudaOps` has no CPU path.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def _excl_cumsum(t: torch.Tensor, dim: int = 0) -> torch.Tensor:
+    return torch.cumsum(t, dim) - t
+
+
+@dataclass
+class ExchangePlan:
+    """Where every entry goes and where every received entry lands.
+
+    send_splits[d]   entries this rank sends to rank d (sorted entries are contiguous per rank)
+    recv_splits[s]   entries arriving from rank s (arrival order: by source rank, then local expert)
+    local_counts[e]  population of local expert e over all sources
+    dst_row[i]       row of arrival i in the padded row space (every expert starts at a multiple of 128)
+    rows_cap         rows of that space (a multiple of 128)
+    """
+    send_splits: list
+    recv_splits: list
+    local_counts: torch.Tensor
+    dst_row: torch.Tensor
+    rows_cap: int
+
+    @staticmethod
+    def build(counts: torch.Tensor, world: int, group=None, tile: int = 128) -> "ExchangePlan":
+        """counts: int32/int64 [E] entries of this rank per GLOBAL expert."""
+        E = counts.numel()
+        assert E % world == 0, "experts must divide evenly over the ranks"
+        e_local = E // world
+        send_mat = counts.reshape(world, e_local).to(torch.int64).contiguous()
+        recv_mat = torch.empty_like(send_mat)
+        if world > 1:
+            dist.all_to_all_single(recv_mat, send_mat, group=group)
+        else:
+            recv_mat.copy_(send_mat)
+        return ExchangePlan.from_matrices(send_mat, recv_mat, tile)
+
+    @staticmethod
+    def from_matrices(send_mat: torch.Tensor, recv_mat: torch.Tensor, tile: int = 128) -> "ExchangePlan":
+        """send_mat [N, E/N]: my entries per (destination, its local expert); recv_mat [N, E/N]: entries
+        per (source, my local expert)."""
+        local_counts = recv_mat.sum(0)
+        padded = (local_counts + tile - 1) // tile * tile
+        pad_offsets = _excl_cumsum(padded)
+        within = _excl_cumsum(recv_mat, 0)                         # rows of expert e that earlier sources fill
+        block_dst = (pad_offsets[None, :] + within).reshape(-1)    # arrival blocks: source major, expert minor
+        block_cnt = recv_mat.reshape(-1)
+        block_start = _excl_cumsum(block_cnt)
+        n_recv = int(block_cnt.sum())                              # host sync: the split sizes are host data
+        dst_row = torch.repeat_interleave(block_dst - block_start, block_cnt, output_size=n_recv) \
+            + torch.arange(n_recv, device=recv_mat.device)
+        return ExchangePlan(send_splits=send_mat.sum(1).tolist(), recv_splits=recv_mat.sum(1).tolist(),
+                            local_counts=local_counts.to(torch.int32), dst_row=dst_row.to(torch.int32),
+                            rows_cap=max(int(padded.sum()), tile))
+
+
+def _all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, world: int, group=None) -> torch.Tensor:
+    """Exchange of row blocks; rows are moved as bytes so that every backend accepts the dtype."""
+    row_bytes = send.shape[1] * send.element_size()
+    send_b = send.contiguous().view(torch.uint8).reshape(-1, row_bytes)
+    recv_b = torch.empty(sum(recv_splits), row_bytes, dtype=torch.uint8, device=send.device)
+    if world > 1:
+        dist.all_to_all_single(recv_b, send_b, output_split_sizes=list(recv_splits),
+                               input_split_sizes=list(send_splits), group=group)
+    else:
+        recv_b.copy_(send_b)
+    return recv_b.view(send.dtype).reshape(-1, send.shape[1])
+
+
+def ep_moe_forward(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
+    """One layer call on this rank; `ops` supplies the compute (see CudaOps for the contract)."""
+    idx, w = ops.route(x)
+    counts, inv_perm = ops.permute(idx)                    # per global expert; sorted position per entry
+    rows, scales = ops.quant_rows(x, inv_perm)             # [T*k, H] e4m3 bytes, [T*k, H/128] fp32, sorted
+    plan = ExchangePlan.build(counts, world, group)
+    recv_rows = _all_to_all_rows(rows, plan.send_splits, plan.recv_splits, world, group)
+    recv_scales = _all_to_all_rows(scales, plan.send_splits, plan.recv_splits, world, group)
+    shared = ops.shared_expert(x)                          # independent of the exchange
+    y_recv = ops.expert_ffn(recv_rows, recv_scales, plan)  # bf16 [n_recv, H] in arrival order
+    y_back = _all_to_all_rows(y_recv, plan.recv_splits, plan.send_splits, world, group)
+    return ops.combine(y_back, inv_perm, w, shared)
+
+
+class CudaOps:
+    """The compute steps on this rank's GPU, through the C ABI. Weights are this rank's expert block."""
+
+    def __init__(self, router_w, router_bias, w13_q, w13_s, w2_q, w2_s, shared=None, k=8, routing=1, n_group=8,
+                 topk_group=4, scaling=1.0, num_experts=None):
+        from . import capi
+        self.capi = capi
+        capi.lib()
+        self.router_w, self.router_bias = router_w, router_bias
+        self.w13_q, self.w13_s, self.w2_q, self.w2_s = w13_q.view(torch.uint8), w13_s, w2_q.view(torch.uint8), w2_s
+        self.shared = None if shared is None else tuple(
+            t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t for t in shared)
+        self.k, self.routing, self.n_group, self.topk_group, self.scaling = k, routing, n_group, topk_group, scaling
+        self.E = num_experts if num_experts is not None else router_w.shape[0]
+        self.e_local = w13_q.shape[0]
+        self.H, self.I = w2_q.shape[1], w2_q.shape[2]
+        self.dev = router_w.device
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+
+    # -- routing and local layout
+    def route(self, x):
+        T = x.shape[0]
+        logits = torch.empty(T, self.E, device=self.dev)
+        self.capi.moe_router_logits(logits, x, self.router_w)
+        idx = torch.empty(T, self.k, dtype=torch.int32, device=self.dev)
+        w = torch.empty(T, self.k, device=self.dev)
+        if self.routing == 0:
+            self.capi.moe_route_softmax_topk(idx, w, logits)
+        else:
+            self.capi.moe_route_sigmoid_group_topk(idx, w, logits, self.router_bias, self.n_group, self.topk_group,
+                                                   self.scaling)
+        return idx, w
+
+    def permute(self, idx):
+        tables = self.capi.moe_permute(idx, self.E)
+        return tables["counts"], tables["inv_perm"]
+
+    def quant_rows(self, x, inv_perm):
+        n = inv_perm.numel()
+        rows = torch.empty(n, self.H, dtype=torch.uint8, device=self.dev)
+        scales = torch.empty(n, self.H // 128, device=self.dev)
+        self.capi.moe_quant_rows(rows, scales, x, inv_perm, self.k)
+        return rows, scales
+
+    # -- experts
+    def _ffn(self, a_q, a_s, w13_q, w13_s, w2_q, w2_s, tile_expert, num_tiles, max_tiles, status):
+        cap, I, H = a_q.shape[0], self.I, self.H
+        h_q = torch.empty(cap, I, dtype=torch.uint8, device=self.dev)
+        h_s = torch.empty(I // 128, cap, device=self.dev)
+        y = torch.empty(cap, H, dtype=torch.bfloat16, device=self.dev)
+        self.capi.moe_grouped_gemm_fp8(0, h_q, h_s, a_q, a_s, w13_q, w13_s, tile_expert, num_tiles, max_tiles,
+                                       status[0:1])
+        self.capi.moe_grouped_gemm_fp8(1, y, None, h_q, h_s, w2_q, w2_s, tile_expert, num_tiles, max_tiles,
+                                       status[1:2])
+        return y
+
+    def expert_ffn(self, recv_rows, recv_scales, plan: ExchangePlan):
+        cap, n = plan.rows_cap, recv_rows.shape[0]
+        i32 = dict(dtype=torch.int32, device=self.dev)
+        a_q = torch.empty(cap, self.H, dtype=torch.uint8, device=self.dev)
+        a_s = torch.empty(self.H // 128, cap, device=self.dev)
+        self.capi.moe_scatter_rows(a_q, a_s, recv_rows, recv_scales, plan.dst_row)
+        max_tiles = cap // 128
+        offsets, pad_offsets = torch.empty(self.e_local + 1, **i32), torch.empty(self.e_local + 1, **i32)
+        tile_expert, num_tiles = torch.empty(max_tiles, **i32), torch.empty(1, **i32)
+        self.capi.moe_tiles_from_counts(plan.local_counts.to(self.dev), offsets, pad_offsets, tile_expert, num_tiles)
+        y = self._ffn(a_q, a_s, self.w13_q, self.w13_s, self.w2_q, self.w2_s, tile_expert, num_tiles, max_tiles,
+                      self.status[0:2])
+        y_recv = torch.empty(n, self.H, dtype=torch.bfloat16, device=self.dev)
+        self.capi.moe_gather_rows(y_recv, y, plan.dst_row)
+        return y_recv
+
+    def shared_expert(self, x):
+        if self.shared is None:
+            return None
+        w13_q, w13_s, w2_q, w2_s = self.shared
+        T = x.shape[0]
+        tiles = (T + 127) // 128
+        a_q = torch.empty(tiles * 128, self.H, dtype=torch.uint8, device=self.dev)
+        a_s = torch.empty(self.H // 128, tiles * 128, device=self.dev)
+        self.capi.moe_quant_dispatch(a_q, a_s, x, None, 1)
+        return self._ffn(a_q, a_s, w13_q.unsqueeze(0), w13_s.unsqueeze(0), w2_q.unsqueeze(0), w2_s.unsqueeze(0),
+                         None, None, tiles, self.status[2:4])
+
+    def combine(self, y_back, inv_perm, w, shared):
+        T = w.shape[0]
+        out = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.dev)
+        self.capi.moe_combine(out, y_back, inv_perm, w, shared)
+        return out

@@ -149,6 +149,25 @@ int moe_quant_dispatch_launcher(cab_e4m3* a_q, float* scales_t, const cab_bf16* 
                                 const int* dst_row, int T, int H, int k, int ld_rows, int config,
                                 cab_stream_t stream);
 
+/* Expert-parallel row movement (the reference has no counterpart; slot as above). */
+/* moe_quant_rows: as moe_quant_dispatch, but the scales are written row-major,     */
+/*   scales[row * (H/128) + block], the layout a row is sent in.                    */
+/* moe_scatter_rows: rows[i] (e4m3 [n,H]) and scales[i] (fp32 [n,H/128]) received     */
+/*   from other ranks -> a_q[dst_row[i]] and scales_t[block*ld_rows + dst_row[i]];    */
+/*   dst_row[i] < 0 skips the row.                                                   */
+/* moe_gather_rows: out[i,:] = y[src_row[i],:] (bf16 [*,H]); src_row[i] < 0 -> zeros. */
+/* moe_tiles_from_counts: offsets, 128-padded offsets, tile_expert[] and num_tiles    */
+/*   from per-expert populations counts[E] (device memory), as moe_permute derives    */
+/*   them from the routing.                                                          */
+int moe_quant_rows_launcher(cab_e4m3* rows_q, float* scales, const cab_bf16* x, const int* dst_row, int T,
+                            int H, int k, int config, cab_stream_t stream);
+int moe_scatter_rows_launcher(cab_e4m3* a_q, float* scales_t, const cab_e4m3* rows, const float* scales,
+                              const int* dst_row, int n, int H, int ld_rows, int config, cab_stream_t stream);
+int moe_gather_rows_launcher(cab_bf16* out, const cab_bf16* y, const int* src_row, int n, int H, int config,
+                             cab_stream_t stream);
+int moe_tiles_from_counts_launcher(const int* counts, int E, int* offsets, int* pad_offsets, int* tile_expert,
+                                   int* num_tiles, int max_tiles, int config, cab_stream_t stream);
+
 /* out[t,:] (bf16) = sum over slot = 0..k-1, in that order, of                   */
 /* weights[t,slot] * y[dst_row[t*k+slot], :] (+ extra[t,:] when non-NULL), fp32   */
 /* accumulation. y, extra, out are bf16 with row length H (H % 8 == 0).           */
