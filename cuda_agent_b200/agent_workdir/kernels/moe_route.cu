@@ -25,7 +25,7 @@ constexpr int kSlots = kMaxE / 32;
 constexpr int kMaxTopK = 32;
 
 // ------------------------------------------------------------------ logits
-// One warp computes 16 tokens x (up to) 64 experts per pass with mma.sync
+// A warp computes 16-token row tiles x (up to) 64 experts per pass with mma.sync
 // m16n8k16 bf16 (fp32 accumulate). Fragments come straight from global memory:
 // a lane reads 16 contiguous bytes (8 bf16) of its A rows and of its B row and
 // feeds them to two MMAs. That assigns the k index inside a 32-wide chunk in a
@@ -40,47 +40,75 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uin
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(128)
+// CTA = 8 warps on MT*16 tokens and (per pass) 64 experts; warp w sums the k range
+// [w*H/8, (w+1)*H/8) (split-K inside the CTA, so that T/16 row tiles still fill the GPU and every
+// warp has many independent 16-byte loads in flight); the 8 partial tiles are added in warp order
+// through shared memory, which keeps the result independent of scheduling.
+template <int MT>
+__global__ void __launch_bounds__(256)
 router_logits_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
                      const __nv_bfloat16* __restrict__ wr, int T, int H, int E) {
-  const int lane = threadIdx.x & 31;
-  const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int t0 = warp_global * 16;
-  if (t0 >= T) return;
+  __shared__ float part[8][16][64 + 1];   // one 16-token row tile at a time
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t0 = blockIdx.x * (MT * 16);
   const int r = lane >> 2;          // fragment row within 8
   const int kq = (lane & 3) * 8;    // this lane's 8 consecutive k inside a 32-chunk
-  const int ta = min(t0 + r, T - 1), tb = min(t0 + r + 8, T - 1);
-  const uint4* xa = reinterpret_cast<const uint4*>(x + (size_t)ta * H + kq);
-  const uint4* xb = reinterpret_cast<const uint4*>(x + (size_t)tb * H + kq);
-
+  const int kchunks = H / 32;
+  const int c_begin = (kchunks * warp) / 8, c_end = (kchunks * (warp + 1)) / 8;
+  const uint4* xa[MT];
+  const uint4* xb[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    xa[m] = reinterpret_cast<const uint4*>(x + (size_t)min(t0 + m * 16 + r, T - 1) * H + kq);
+    xb[m] = reinterpret_cast<const uint4*>(x + (size_t)min(t0 + m * 16 + r + 8, T - 1) * H + kq);
+  }
   for (int e0 = 0; e0 < E; e0 += 64) {
     const int ntiles = min(8, (E - e0) >> 3);
-    float acc[8][4];
+    float acc[MT][8][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f;
     const __nv_bfloat16* wbase = wr + (size_t)(e0 + r) * H + kq;
-    for (int k0 = 0; k0 < H; k0 += 32) {
-      const uint4 a_lo = __ldg(xa + (k0 >> 3));
-      const uint4 a_hi = __ldg(xb + (k0 >> 3));
+#pragma unroll 2
+    for (int c = c_begin; c < c_end; ++c) {
+      uint4 a_lo[MT], a_hi[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) { a_lo[m] = __ldg(xa[m] + c * 4); a_hi[m] = __ldg(xb[m] + c * 4); }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (j < ntiles) {
-          const uint4 b = __ldg(reinterpret_cast<const uint4*>(wbase + (size_t)j * 8 * H + k0));
-          mma_bf16_16x8x16(acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-          mma_bf16_16x8x16(acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+          const uint4 b = __ldg(reinterpret_cast<const uint4*>(wbase + (size_t)j * 8 * H + c * 32));
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            mma_bf16_16x8x16(acc[m][j], a_lo[m].x, a_hi[m].x, a_lo[m].y, a_hi[m].y, b.x, b.y);
+            mma_bf16_16x8x16(acc[m][j], a_lo[m].z, a_hi[m].z, a_lo[m].w, a_hi[m].w, b.z, b.w);
+          }
         }
       }
     }
     const int col = (lane & 3) * 2;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < ntiles) {
-        const int e = e0 + j * 8 + col;
-        if (t0 + r < T)
-          *reinterpret_cast<float2*>(logits + (size_t)(t0 + r) * E + e) = make_float2(acc[j][0], acc[j][1]);
-        if (t0 + r + 8 < T)
-          *reinterpret_cast<float2*>(logits + (size_t)(t0 + r + 8) * E + e) = make_float2(acc[j][2], acc[j][3]);
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        part[warp][r][j * 8 + col] = acc[m][j][0];
+        part[warp][r][j * 8 + col + 1] = acc[m][j][1];
+        part[warp][r + 8][j * 8 + col] = acc[m][j][2];
+        part[warp][r + 8][j * 8 + col + 1] = acc[m][j][3];
       }
+      __syncthreads();
+      for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+        const int row = i >> 6, e = i & 63;
+        const int t = t0 + m * 16 + row;
+        if (t < T && e < ntiles * 8) {
+          float sum = 0.f;
+#pragma unroll
+          for (int w = 0; w < 8; ++w) sum += part[w][row][e];
+          logits[(size_t)t * E + e0 + e] = sum;
+        }
+      }
+      __syncthreads();
     }
   }
 }
@@ -229,10 +257,13 @@ extern "C" int moe_router_logits_launcher(float* logits, const cab_bf16* x, cons
   if (T < 0 || H <= 0 || E <= 0 || H % 32 != 0 || E % 8 != 0) return CAB_ERR_BAD_ARGUMENT;
   if (!cab::aligned_to(x, 16) || !cab::aligned_to(wr, 16) || !cab::aligned_to(logits, 8))
     return CAB_ERR_MISALIGNED;
-  const int warps = (T + 15) / 16;
-  router_logits_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(
-      logits, reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(wr),
-      T, H, E);
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(wr);
+  // 32 tokens per CTA (each weight fragment feeds two row tiles) once that still gives two CTAs per SM
+  if (T >= 32 * 2 * cab::kNumSMs)
+    router_logits_kernel<2><<<(T + 31) / 32, 256, 0, stream>>>(logits, xp, wp, T, H, E);
+  else
+    router_logits_kernel<1><<<(T + 15) / 16, 256, 0, stream>>>(logits, xp, wp, T, H, E);
   return cab::launch_status();
 }
 
