@@ -41,6 +41,45 @@ __device__ __forceinline__ void chunk_warp_counts(int (*wc)[kMaxE], const int* _
   __syncthreads();
 }
 
+// Offsets, 128-padded offsets and the tile table from per-expert populations held in shared memory
+// (cnt[e], e < E <= 256), by all threads of the CTA: a warp-shuffle scan over the experts, then every
+// expert writes its own run of tile_expert[].
+__device__ void build_tile_table(const int* cnt, int E, int* __restrict__ offsets, int* __restrict__ pad_offsets,
+                                 int* __restrict__ tile_expert, int* __restrict__ num_tiles, int max_tiles,
+                                 int* __restrict__ status, int* scan_sm /* 2 * 8 ints */) {
+  __shared__ int total_tiles;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = tid < E ? cnt[tid] : 0;
+  const int nt = (c + kTileM - 1) / kTileM;
+  int inc_c = c, inc_t = nt;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, inc_c, off), b = __shfl_up_sync(0xffffffffu, inc_t, off);
+    if (lane >= off) { inc_c += a; inc_t += b; }
+  }
+  if (warp < 8 && lane == 31) { scan_sm[warp] = inc_c; scan_sm[8 + warp] = inc_t; }
+  __syncthreads();
+  int base_c = 0, base_t = 0;
+  for (int w = 0; w < warp && w < 8; ++w) { base_c += scan_sm[w]; base_t += scan_sm[8 + w]; }
+  const int off_c = base_c + inc_c - c, off_t = base_t + inc_t - nt;     // exclusive
+  if (tid < E) {
+    offsets[tid] = off_c;
+    pad_offsets[tid] = off_t * kTileM;
+    for (int j = 0; j < nt; ++j)
+      if (off_t + j < max_tiles) tile_expert[off_t + j] = tid;
+  }
+  if (tid == E - 1) {
+    const int tiles = off_t + nt;
+    offsets[E] = off_c + c;
+    pad_offsets[E] = tiles * kTileM;
+    if (tiles > max_tiles && status) atomicExch(status, 2);
+    num_tiles[0] = min(tiles, max_tiles);
+    total_tiles = min(tiles, max_tiles);
+  }
+  __syncthreads();
+  for (int j = total_tiles + tid; j < max_tiles; j += blockDim.x) tile_expert[j] = -1;
+}
+
 // Kernel 1: per-chunk expert counts; the last CTA to finish turns them into
 // chunk bases, expert offsets, padded offsets and the tile table.
 __global__ void __launch_bounds__(kChunk)
@@ -80,25 +119,8 @@ moe_count_scan_kernel(const int* __restrict__ idx, int n, int E, int nchunks,
     wc[0][e] = run;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int off = 0, pad = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
-      const int c = wc[0][e];
-      offsets[e] = off;
-      pad_offsets[e] = pad;
-      const int nt = (c + kTileM - 1) / kTileM;
-      for (int j = 0; j < nt && tiles + j < max_tiles; ++j) tile_expert[tiles + j] = e;
-      off += c;
-      pad += nt * kTileM;
-      tiles += nt;
-    }
-    offsets[E] = off;
-    pad_offsets[E] = pad;
-    if (tiles > max_tiles && status) atomicExch(status, 2);
-    num_tiles[0] = min(tiles, max_tiles);
-    for (int j = min(tiles, max_tiles); j < max_tiles; ++j) tile_expert[j] = -1;
-    *done_counter = 0;   // ready for the next call
-  }
+  build_tile_table(wc[0], E, offsets, pad_offsets, tile_expert, num_tiles, max_tiles, status, &wc[1][0]);
+  if (threadIdx.x == 0) *done_counter = 0;   // ready for the next call
 }
 
 // Kernel 2: position of every entry.
@@ -252,23 +274,15 @@ moe_gather_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ y, con
 
 // Tile table of the local experts from their populations (what moe_count_scan_kernel derives from
 // the routing when everything is local).
-__global__ void moe_tiles_from_counts_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets,
-                                             int* __restrict__ pad_offsets, int* __restrict__ tile_expert,
-                                             int* __restrict__ num_tiles, int max_tiles) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int off = 0, pad = 0, tiles = 0;
-  for (int e = 0; e < E; ++e) {
-    const int c = counts[e];
-    offsets[e] = off;
-    pad_offsets[e] = pad;
-    const int nt = (c + kTileM - 1) / kTileM;
-    for (int j = 0; j < nt && tiles + j < max_tiles; ++j) tile_expert[tiles + j] = e;
-    off += c; pad += nt * kTileM; tiles += nt;
-  }
-  offsets[E] = off;
-  pad_offsets[E] = pad;
-  num_tiles[0] = min(tiles, max_tiles);
-  for (int j = min(tiles, max_tiles); j < max_tiles; ++j) tile_expert[j] = -1;
+__global__ void __launch_bounds__(256)
+moe_tiles_from_counts_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets,
+                             int* __restrict__ pad_offsets, int* __restrict__ tile_expert,
+                             int* __restrict__ num_tiles, int max_tiles) {
+  __shared__ int cnt[kMaxE];
+  __shared__ int scan_sm[16];
+  if (threadIdx.x < E) cnt[threadIdx.x] = counts[threadIdx.x];
+  __syncthreads();
+  build_tile_table(cnt, E, offsets, pad_offsets, tile_expert, num_tiles, max_tiles, nullptr, scan_sm);
 }
 
 }  // namespace
@@ -379,6 +393,7 @@ extern "C" int moe_tiles_from_counts_launcher(const int* counts, int E, int* off
   (void)config;
   if (!counts || !offsets || !pad_offsets || !tile_expert || !num_tiles || E <= 0 || max_tiles <= 0)
     return CAB_ERR_BAD_ARGUMENT;
-  moe_tiles_from_counts_kernel<<<1, 32, 0, stream>>>(counts, E, offsets, pad_offsets, tile_expert, num_tiles, max_tiles);
+  if (E > kMaxE) return CAB_ERR_TOO_LARGE;
+  moe_tiles_from_counts_kernel<<<1, 256, 0, stream>>>(counts, E, offsets, pad_offsets, tile_expert, num_tiles, max_tiles);
   return cab::launch_status();
 }

@@ -259,9 +259,10 @@ extern "C" int moe_router_logits_launcher(float* logits, const cab_bf16* x, cons
     return CAB_ERR_MISALIGNED;
   const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
   const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(wr);
-  // 32 tokens per CTA (each weight fragment feeds two row tiles) once that still gives two CTAs per SM
-  if (T >= 32 * 2 * cab::kNumSMs)
-    router_logits_kernel<2><<<(T + 31) / 32, 256, 0, stream>>>(logits, xp, wp, T, H, E);
+  // Every CTA reads the whole router weight, so a large weight (E*H) wants many tokens per CTA: 64
+  // (each weight fragment feeds four row tiles) once the weight exceeds 1 MB, else 16.
+  if ((size_t)E * H * 2 >= (1u << 20) && T >= 64 * 32)
+    router_logits_kernel<4><<<(T + 63) / 64, 256, 0, stream>>>(logits, xp, wp, T, H, E);
   else
     router_logits_kernel<1><<<(T + 15) / 16, 256, 0, stream>>>(logits, xp, wp, T, H, E);
   return cab::launch_status();
