@@ -430,15 +430,29 @@ def run_mla(args):
     back (the KV cache is resident, as in serving). The cache (2.4 GB) exceeds L2; the 2048 rows a step
     touches per sequence are 151 MB in total, also above L2, so no flush is needed."""
     import torch
+    import torch.distributed as dist
     from cuda_agent_b200.benchmarks import MlaWorkload, time_cuda
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    wl = MlaWorkload(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    wl = MlaWorkload(dev, seed=1236 + rank)
     steps, warmup = min(args.steps, 200), max(3, min(args.warmup, 20))
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
     w0 = time.monotonic()
-    ms = time_cuda(lambda: wl.step(args.nsplit, args.config), steps, warmup)
+
+    def timed(fn):
+        """ms per call: CUDA events between barriers, max over ranks."""
+        if world > 1:
+            dist.barrier()
+        t = torch.tensor([time_cuda(fn, steps, warmup)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    ms = timed(lambda: wl.step(args.nsplit, args.config))
     hq, hidx, hlen = wl.q.cpu().pin_memory(), wl.idx.cpu().pin_memory(), wl.seq_len.cpu().pin_memory()
     ho = torch.empty(wl.out.shape, dtype=torch.bfloat16).pin_memory()
     dq, didx, dlen = torch.empty_like(wl.q), torch.empty_like(wl.idx), torch.empty_like(wl.seq_len)
@@ -446,24 +460,30 @@ def run_mla(args):
     def e2e_step():
         dq.copy_(hq, non_blocking=True); didx.copy_(hidx, non_blocking=True); dlen.copy_(hlen, non_blocking=True)
         ho.copy_(wl.api_step(dq, didx, dlen), non_blocking=True)
-    ms_e2e = time_cuda(e2e_step, steps, warmup)
+    ms_e2e = timed(e2e_step)
     windows = [(w0, time.monotonic())]
     sampler.stop()
     assert int(wl.status) == 0
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
     peaks_file = ROOT / "MEASURED_PEAKS.json"
     peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0}
     t_roof = max(wl.bytes / (peaks["hbm_gbs"] * 1e9), wl.flops / (peaks["bf16_tflops"] * 1e12))
     gbs = wl.bytes / (ms * 1e-3) / 1e9
     line = {
-        "metric": "sparse_mla_decode_tok_per_s", "value": round(wl.B / (ms * 1e-3), 1), "unit": "tok/s", "n_gpus": 1,
+        "metric": "sparse_mla_decode_tok_per_s", "value": round(wl.B * world / (ms * 1e-3), 1), "unit": "tok/s",
+        "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 (fp32 softmax and accumulation)", "data": "synthetic",
-        "config": {"workload": "sparse_mla_decode", "B": wl.B, "heads": wl.Hh, "S": wl.S, "topk": wl.topk,
+        "config": {"workload": "sparse_mla_decode", "B_per_gpu": wl.B, "heads": wl.Hh, "S": wl.S, "topk": wl.topk,
                    "nsplit": args.nsplit, "bytes": wl.bytes, "flops": wl.flops,
                    "l2": "rows touched per step (151 MB) and the cache (2.4 GB) exceed L2; no flush needed"},
-        "e2e": {"value": round(wl.B / (ms_e2e * 1e-3), 1), "unit": "tok/s",
-                "h2d_bytes_per_step": hq.numel() * 2 + hidx.numel() * 4 + hlen.numel() * 4,
-                "d2h_bytes_per_step": ho.numel() * 2, "ms_per_step": round(ms_e2e, 5),
+        "e2e": {"value": round(wl.B * world / (ms_e2e * 1e-3), 1), "unit": "tok/s",
+                "h2d_bytes_per_step": (hq.numel() * 2 + hidx.numel() * 4 + hlen.numel() * 4) * world,
+                "d2h_bytes_per_step": ho.numel() * 2 * world, "ms_per_step": round(ms_e2e, 5),
                 "api": "cuda_extension.mla_sparse_decode_forward"},
         "gpu_launches": steps * (1 if args.nsplit == 1 else 2),
         "roofline": {"bound": "hbm", "kernel": "mla_sparse_decode_kernel", "achieved": round(gbs, 1),
