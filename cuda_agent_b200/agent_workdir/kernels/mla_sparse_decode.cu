@@ -11,8 +11,8 @@
 //                       O += P . V    : V is the first 512 columns of the same tile read as an
 //                                       MN-major operand, two M=64 N=256 accumulators that share
 //                                       256 tensor-memory columns (lanes 0-15 / 16-31 of each quadrant)
-//                       per block the order is Q.K^T, (softmax), P.V: the stage is released as early
-//                       as possible, the gather of the block after next overlaps the next block
+//                       issue order follows readiness: Q.K^T of block j+1 overlaps the softmax of
+//                       block j when its rows have landed, P.V of block j releases its stage
 //   softmax warps (4)   read S from tensor memory (one head per thread, lanes 0-15 of each warp),
 //                       scale, mask invalid entries, online softmax in the exp2 domain with a lazy
 //                       reference maximum (O is rescaled in tensor memory only when the running
@@ -156,6 +156,21 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
     // Iteration j: publish block j-1 as soon as it has landed (nothing newer is in flight yet), then
     // wait for the stage of block j to be released by P.V of block j-2 and start its copies. Block j is
     // in flight while block j-1 is computed.
+    // Geometry of this lane's 36 pieces (which of the warp's 16 rows, where in the tile, which 16 bytes
+    // of the cache row) does not depend on the block.
+    const int pw = ptid >> 5;
+    int piece_row[36];
+    uint32_t piece_dst[36];
+    int piece_src[36];
+#pragma unroll
+    for (int it = 0; it < 36; ++it) {
+      const int piece = it * 32 + lane;
+      const int rl = piece / 72, c16 = piece - rl * 72;
+      const int r = pw * 16 + rl;
+      piece_row[it] = rl;
+      piece_dst[it] = (c16 >> 3) * kChunkBytes + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
+      piece_src[it] = c16 * 8;
+    }
     for (int j = 0; j <= nb; ++j) {
       if (j >= 1) {
         cp_async_wait<0>();
@@ -167,9 +182,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
       if (j >= 2 && !sm100::mbar_wait_relaxed(&ctl.kv_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kWaitKvEmpty))
         break;
       // Warp w of the producers owns rows 16w..16w+15 of the block: lane l fetches the cache row
-      // number of row 16w + (l & 15) once, the 1152 sixteen-byte pieces of the 16 rows are then
-      // spread over the lanes (36 each) and every piece learns its row by shuffle.
-      const int pw = ptid >> 5;
+      // number of row 16w + (l & 15) once, the 1152 sixteen-byte pieces of the 16 rows are spread over
+      // the lanes (36 each) and every piece learns its row by shuffle.
       const int my_i = (j0 + j) * kTok + pw * 16 + (lane & 15);
       const int my_t = my_i < p.topk ? __ldg(idx_b + my_i) : -1;
       const bool my_ok = my_t >= 0 && my_t < len;
@@ -177,14 +191,10 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
       // an invalid entry copies row 0: finite data that the mask multiplies by zero
       const int my_row = my_ok ? my_t : 0;
       const uint32_t dst = sm100::smem_u32(kv_tile + st * kTileBytes);
-#pragma unroll 4
+#pragma unroll
       for (int it = 0; it < 36; ++it) {
-        const int piece = it * 32 + lane;
-        const int rl = piece / 72, c16 = piece - rl * 72;
-        const int t = __shfl_sync(0xffffffffu, my_row, rl);
-        const int r = pw * 16 + rl;
-        cp_async_16(dst + (c16 >> 3) * kChunkBytes + r * 128 + (((c16 & 7) ^ (r & 7)) << 4),
-                    kv_b + (size_t)t * kDqk + c16 * 8);
+        const int t = __shfl_sync(0xffffffffu, my_row, piece_row[it]);
+        cp_async_16(dst + piece_dst[it], kv_b + (size_t)t * kDqk + piece_src[it]);
       }
       cp_async_commit();
     }
@@ -212,26 +222,48 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
         sm100::umma_commit(&ctl.kv_empty[st]);
         sm100::umma_commit(&ctl.p_empty);
       };
-      for (int j = 0; j < nb && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!sm100::mbar_wait(&ctl.kv_full[st], ph, abort_flag, p.status, kWaitKvFull)) { ok = false; break; }
-        if (!sm100::mbar_wait(&ctl.s_empty[st], ph ^ 1, abort_flag, p.status, kWaitSEmpty)) { ok = false; break; }
-        sm100::tc_fence_after_sync();
-        const uint32_t k_addr = sm100::smem_u32(kv_tile + st * kTileBytes);
+      // Issue order is decided by what is ready: Q.K^T of the next block as soon as its rows have landed
+      // (at most one block ahead of P.V, so that the softmax of block j overlaps Q.K^T of block j+1),
+      // otherwise P.V of the oldest block whose P is written. The stage of block j is released by its
+      // P.V, and the gather of block j+2 goes into it.
+      int next_qk = 0, next_pv = 0;
+      const long long t_start = clock64();
+      uint32_t spin = 0;
+      while (next_pv < nb && ok) {
+        bool issued = false;
+        if (next_qk < nb && next_qk <= next_pv + 1) {
+          const int j = next_qk, st = j & 1;
+          const uint32_t ph = (j >> 1) & 1;
+          if (sm100::mbar_try_wait(&ctl.kv_full[st], ph) && sm100::mbar_try_wait(&ctl.s_empty[st], ph ^ 1)) {
+            sm100::tc_fence_after_sync();
+            const uint32_t k_addr = sm100::smem_u32(kv_tile + st * kTileBytes);
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const uint64_t a = umma_desc_sw128(q_addr + c * kChunkBytes, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(k_addr + c * kChunkBytes, 16, 1024);
+            for (int c = 0; c < kChunks; ++c) {
+              const uint64_t a = umma_desc_sw128(q_addr + c * kChunkBytes, 16, 1024);
+              const uint64_t bd = umma_desc_sw128(k_addr + c * kChunkBytes, 16, 1024);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4)
-            sm100::umma_f16(tmem_base + kColS + st * kTok, a + 2 * k4, bd + 2 * k4, idesc_qk, (c > 0 || k4 > 0) ? 1u : 0u);
+              for (int k4 = 0; k4 < 4; ++k4)
+                sm100::umma_f16(tmem_base + kColS + st * kTok, a + 2 * k4, bd + 2 * k4, idesc_qk, (c > 0 || k4 > 0) ? 1u : 0u);
+            }
+            sm100::umma_commit(&ctl.s_full[st]);
+            ++next_qk;
+            issued = true;
+          }
         }
-        sm100::umma_commit(&ctl.s_full[st]);
-        // P.V of the same block follows at once: with two K/V stages the stage of block j can only be
-        // refilled after this P.V, so issuing it before the next Q.K^T is what lets the gather of
-        // block j+2 start while block j+1 is computed.
-        issue_pv(j);
+        if (!issued && next_pv < next_qk && sm100::mbar_try_wait(&ctl.p_full, next_pv & 1)) {
+          issue_pv(next_pv);
+          ++next_pv;
+          issued = true;
+        }
+        if (issued) { spin = 0; continue; }
+        if ((++spin & 0x3ff) == 0) {
+          if (*abort_flag) { ok = false; break; }
+          if (clock64() - t_start > (long long)(nb + 2) * sm100::kWaitLimitCycles) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, kWaitKvFull);
+            ok = false;
+          }
+        }
       }
       if (ok) sm100::umma_commit(&ctl.o_done);
     }
