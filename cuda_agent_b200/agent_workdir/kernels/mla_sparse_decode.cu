@@ -292,15 +292,18 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
       // validity of the block's 64 entries as two ballots
       const unsigned v_lo = __ballot_sync(0xffffffffu, ctl.valid[st][lane] != 0);
       const unsigned v_hi = __ballot_sync(0xffffffffu, ctl.valid[st][lane + 32] != 0);
-      float s[kTok];
-      float m_blk = -INFINITY;
+      // masked raw scores stay in the registers the tensor-memory load filled; the softmax scale is
+      // folded into the exponent: p = exp2(raw * scale_log2 - m)
+      float m_raw = -INFINITY;
 #pragma unroll
       for (int i = 0; i < kTok; ++i) {
-        const float raw = __uint_as_float(i < 32 ? t0[i] : t1[i - 32]);
+        uint32_t& slot = i < 32 ? t0[i] : t1[i - 32];
         const bool live = row_ok && (((i < 32 ? v_lo : v_hi) >> (i & 31)) & 1u);
-        s[i] = live ? raw * p.scale_log2 : -INFINITY;
-        m_blk = fmaxf(m_blk, s[i]);
+        const float raw = live ? __uint_as_float(slot) : -INFINITY;
+        slot = __float_as_uint(raw);
+        m_raw = fmaxf(m_raw, raw);
       }
+      const float m_blk = m_raw * p.scale_log2;            // scale > 0: the maximum commutes with it
       // lazy reference maximum: move it only on the first non-empty block or on a jump > 2^8
       float factor = 1.f;
       if (m_blk > -INFINITY) {
@@ -311,12 +314,14 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
           m_ref = m_blk;
         }
       }
-      const float m_sub = m_ref == -INFINITY ? 0.f : m_ref;   // exp2(-inf - m_sub) = 0 for masked entries
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;   // exp2(-inf) = 0 for masked entries
       float psum = 0.f;
       uint32_t packed[kTok / 2];
 #pragma unroll
       for (int i = 0; i < kTok; i += 2) {
-        const float p0 = exp2f(s[i] - m_sub), p1 = exp2f(s[i + 1] - m_sub);
+        const float r0 = __uint_as_float(i < 32 ? t0[i] : t1[i - 32]);
+        const float r1 = __uint_as_float(i + 1 < 32 ? t0[i + 1] : t1[i + 1 - 32]);
+        const float p0 = exp2f(fmaf(r0, p.scale_log2, neg_m)), p1 = exp2f(fmaf(r1, p.scale_log2, neg_m));
         psum += p0 + p1;
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
