@@ -100,12 +100,16 @@ def ep_moe_forward(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor
     idx, w = ops.route(x)
     counts, inv_perm = ops.permute(idx)                    # per global expert; sorted position per entry
     rows, scales = ops.quant_rows(x, inv_perm)             # [T*k, H] e4m3 bytes, [T*k, H/128] fp32, sorted
+    # The shared expert depends on nothing that is exchanged: ops that can, start it now on a side
+    # stream so that it runs under the population exchange and the dispatch.
+    begin = getattr(ops, "shared_expert_begin", None)
+    pending = begin(x) if begin else None
     plan = ExchangePlan.build(counts, world, group)
     recv_rows = _all_to_all_rows(rows, plan.send_splits, plan.recv_splits, world, group)
     recv_scales = _all_to_all_rows(scales, plan.send_splits, plan.recv_splits, world, group)
-    shared = ops.shared_expert(x)                          # independent of the exchange
     y_recv = ops.expert_ffn(recv_rows, recv_scales, plan)  # bf16 [n_recv, H] in arrival order
     y_back = _all_to_all_rows(y_recv, plan.recv_splits, plan.send_splits, world, group)
+    shared = ops.shared_expert_end(pending) if begin else ops.shared_expert(x)
     return ops.combine(y_back, inv_perm, w, shared)
 
 
@@ -127,6 +131,7 @@ class CudaOps:
         self.H, self.I = w2_q.shape[1], w2_q.shape[2]
         self.dev = router_w.device
         self.status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        self._side = None
 
     # -- routing and local layout
     def route(self, x):
@@ -192,6 +197,27 @@ class CudaOps:
         self.capi.moe_quant_dispatch(a_q, a_s, x, None, 1)
         return self._ffn(a_q, a_s, w13_q.unsqueeze(0), w13_s.unsqueeze(0), w2_q.unsqueeze(0), w2_s.unsqueeze(0),
                          None, None, tiles, self.status[2:4])
+
+    def shared_expert_begin(self, x):
+        """Shared expert on a side stream; returns what shared_expert_end needs to join it."""
+        if self.shared is None:
+            return None
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.dev)
+        cur = torch.cuda.current_stream(self.dev)
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):
+            y = self.shared_expert(x)
+            x.record_stream(self._side)
+        return y
+
+    def shared_expert_end(self, pending):
+        if pending is None:
+            return None
+        cur = torch.cuda.current_stream(self.dev)
+        cur.wait_stream(self._side)
+        pending.record_stream(cur)
+        return pending
 
     def combine(self, y_back, inv_perm, w, shared):
         T = w.shape[0]
