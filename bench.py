@@ -63,6 +63,8 @@ def parse_args():
     ap.add_argument("--workload", choices=["gdn", "moe", "mla", "moe_ep"], default="gdn",
                     help="gdn = the headline line; moe = FP8 MoE layer (4096 tokens, 64 experts, top-6); "
                          "mla = top-2048 sparse MLA decode (64 sequences, 128 heads)")
+    ap.add_argument("--micro-batches", type=int, default=1,
+                    help="moe_ep: token micro-batches pipelined over streams (with --config C < 148 GEMM CTAs)")
     ap.add_argument("--nsplit", type=int, default=1, help="mla: splits of the selected rows per CTA group")
     return ap.parse_args()
 
@@ -509,7 +511,7 @@ def run_moe_ep(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    wl = MoeEpWorkload(dev, rank, world)
+    wl = MoeEpWorkload(dev, rank, world, micro_batches=args.micro_batches, gemm_ctas=args.config)
     steps, warmup = min(args.steps, 30), max(3, min(args.warmup, 5))
 
     def barrier():

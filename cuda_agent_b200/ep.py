@@ -95,29 +95,90 @@ def _all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, world: int, g
     return recv_b.view(send.dtype).reshape(-1, send.shape[1])
 
 
-def ep_moe_forward(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
-    """One layer call on this rank; `ops` supplies the compute (see CudaOps for the contract)."""
-    idx, w = ops.route(x)
-    counts, inv_perm = ops.permute(idx)                    # per global expert; sorted position per entry
-    rows, scales = ops.quant_rows(x, inv_perm)             # [T*k, H] e4m3 bytes, [T*k, H/128] fp32, sorted
-    # The shared expert depends on nothing that is exchanged: ops that can, start it now on a side
-    # stream so that it runs under the population exchange and the dispatch.
+def ep_moe_forward(x: torch.Tensor, ops, world: int, group=None, micro_batches: int = 1) -> torch.Tensor:
+    """One layer call on this rank; `ops` supplies the compute (see CudaOps for the contract).
+
+    With micro_batches = 2 the local tokens are processed as two halves on two CUDA streams, issued in
+    an interleaved order: the dispatch of the second half travels while the experts work on the first,
+    and the first half's results travel back while the experts work on the second. The result does not
+    depend on the split (every token is computed independently of its neighbours)."""
+    if micro_batches <= 1 or x.shape[0] < 2 * micro_batches:
+        return _ep_pipeline([x], ops, world, group)[0]
+    bounds = [x.shape[0] * i // micro_batches for i in range(micro_batches + 1)]
+    parts = [x[bounds[i]:bounds[i + 1]] for i in range(micro_batches)]
+    return torch.cat(_ep_pipeline(parts, ops, world, group), dim=0)
+
+
+_STREAMS = {}
+
+
+def _part_streams(device, n):
+    key = (device.index, n)
+    if key not in _STREAMS:
+        _STREAMS[key] = [torch.cuda.Stream(device=device) for _ in range(n)]
+    return _STREAMS[key]
+
+
+class _NoStream:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def _ep_pipeline(parts, ops, world: int, group=None):
+    """The layer schedule for each part, stage by stage across parts (part i on its own stream when
+    the tensors live on a GPU), so that exchanges of one part overlap the compute of another."""
+    n = len(parts)
+    on_gpu = parts[0].is_cuda and n > 1
+    if on_gpu:
+        cur = torch.cuda.current_stream(parts[0].device)
+        streams = _part_streams(parts[0].device, n)
+        for st in streams:
+            st.wait_stream(cur)
+    ctx = (lambda i: torch.cuda.stream(streams[i])) if on_gpu else (lambda i: _NoStream())
     begin = getattr(ops, "shared_expert_begin", None)
-    pending = begin(x) if begin else None
-    plan = ExchangePlan.build(counts, world, group)
-    recv_rows = _all_to_all_rows(rows, plan.send_splits, plan.recv_splits, world, group)
-    recv_scales = _all_to_all_rows(scales, plan.send_splits, plan.recv_splits, world, group)
-    y_recv = ops.expert_ffn(recv_rows, recv_scales, plan)  # bf16 [n_recv, H] in arrival order
-    y_back = _all_to_all_rows(y_recv, plan.recv_splits, plan.send_splits, world, group)
-    shared = ops.shared_expert_end(pending) if begin else ops.shared_expert(x)
-    return ops.combine(y_back, inv_perm, w, shared)
+    st = [dict() for _ in range(n)]
+    for i, x in enumerate(parts):                      # local routing, sorting, quantisation
+        with ctx(i):
+            s = st[i]
+            s["idx"], s["w"] = ops.route(x)
+            s["counts"], s["inv_perm"] = ops.permute(s["idx"])
+            s["rows"], s["scales"] = ops.quant_rows(x, s["inv_perm"])
+            # the shared expert depends on nothing that is exchanged: start it now on a side stream
+            s["pending"] = begin(x) if begin else None
+    for i in range(n):                                 # population exchange (host sync) and dispatch
+        with ctx(i):
+            s = st[i]
+            s["plan"] = ExchangePlan.build(s["counts"], world, group)
+            p = s["plan"]
+            s["recv_rows"] = _all_to_all_rows(s["rows"], p.send_splits, p.recv_splits, world, group)
+            s["recv_scales"] = _all_to_all_rows(s["scales"], p.send_splits, p.recv_splits, world, group)
+    for i in range(n):                                 # experts, then the way back
+        with ctx(i):
+            s = st[i]
+            p = s["plan"]
+            y_recv = ops.expert_ffn(s["recv_rows"], s["recv_scales"], p)     # bf16 [n_recv, H], arrival order
+            s["y_back"] = _all_to_all_rows(y_recv, p.recv_splits, p.send_splits, world, group)
+    outs = []
+    for i, x in enumerate(parts):                      # combine
+        with ctx(i):
+            s = st[i]
+            shared = ops.shared_expert_end(s["pending"]) if begin else ops.shared_expert(x)
+            outs.append(ops.combine(s["y_back"], s["inv_perm"], s["w"], shared))
+    if on_gpu:
+        for i, stream in enumerate(streams):
+            cur.wait_stream(stream)
+            outs[i].record_stream(cur)
+    return outs
 
 
 class CudaOps:
     """The compute steps on this rank's GPU, through the C ABI. Weights are this rank's expert block."""
 
     def __init__(self, router_w, router_bias, w13_q, w13_s, w2_q, w2_s, shared=None, k=8, routing=1, n_group=8,
-                 topk_group=4, scaling=1.0, num_experts=None):
+                 topk_group=4, scaling=1.0, num_experts=None, gemm_ctas=0):
         from . import capi
         self.capi = capi
         capi.lib()
@@ -132,6 +193,9 @@ class CudaOps:
         self.dev = router_w.device
         self.status = torch.zeros(4, dtype=torch.int32, device=self.dev)
         self._side = None
+        # persistent CTAs of the grouped GEMMs (0 = one per SM). A GEMM CTA takes a whole SM (registers and
+        # shared memory), so exchanges can only run beside the GEMMs on SMs that are left free.
+        self.gemm_ctas = gemm_ctas
 
     # -- routing and local layout
     def route(self, x):
@@ -165,9 +229,9 @@ class CudaOps:
         h_s = torch.empty(I // 128, cap, device=self.dev)
         y = torch.empty(cap, H, dtype=torch.bfloat16, device=self.dev)
         self.capi.moe_grouped_gemm_fp8(0, h_q, h_s, a_q, a_s, w13_q, w13_s, tile_expert, num_tiles, max_tiles,
-                                       status[0:1])
+                                       status[0:1], self.gemm_ctas)
         self.capi.moe_grouped_gemm_fp8(1, y, None, h_q, h_s, w2_q, w2_s, tile_expert, num_tiles, max_tiles,
-                                       status[1:2])
+                                       status[1:2], self.gemm_ctas)
         return y
 
     def expert_ffn(self, recv_rows, recv_scales, plan: ExchangePlan):

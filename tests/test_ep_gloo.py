@@ -84,6 +84,8 @@ class OracleOps:
 
 
 def _worker(rank, world, port, cfg, result_dir):
+    # cfg 1 also exercises the two-micro-batch schedule (every rank must issue the same collectives)
+
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -96,7 +98,7 @@ def _worker(rank, world, port, cfg, result_dir):
         gen = torch.Generator().manual_seed(100 + rank)
         T = 70 + 13 * rank                                  # ragged: ranks hold different token counts
         x = torch.randn(T, model.H, generator=gen).to(torch.bfloat16)
-        out = ep_moe_forward(x, OracleOps(m, model, rank, world), world)
+        out = ep_moe_forward(x, OracleOps(m, model, rank, world), world, micro_batches=1 + cfg)
         ref = model(x)
         rel = float((out.float() - ref.float()).norm() / ref.float().norm())
         torch.save({"rel": rel, "T": T}, os.path.join(result_dir, f"rank{rank}.pt"))

@@ -49,6 +49,9 @@ def test_world1_matches_oracle_and_fused_op(cuda_device, cfg, T):
                             sd["w2_s"], *sh, model.k, 0 if model.routing == "softmax" else 1, model.n_group,
                             model.topk_group, 1.0, True, 0)
     assert torch.equal(out, fused)                         # same kernels, same row order per expert
+    out2 = ep_moe_forward(x.to(cuda_device), ops, 1, micro_batches=2)   # two halves on two streams
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
 
 
 def _rank_main(rank, world, port, cfg, result_dir):
@@ -64,7 +67,7 @@ def _rank_main(rank, world, port, cfg, result_dir):
         ops = make_ops(model, dev, rank, world)
         T = 200 + 56 * rank
         x = torch.randn(T, model.H, generator=torch.Generator().manual_seed(7 + rank)).to(torch.bfloat16)
-        out = ep_moe_forward(x.to(dev), ops, world)
+        out = ep_moe_forward(x.to(dev), ops, world, micro_batches=1 + cfg)
         torch.cuda.synchronize()
         ref = model(x)
         rel = float((out.float().cpu() - ref.float()).norm() / ref.float().norm())
