@@ -49,7 +49,7 @@ D2H_BYTES = B * HV * D * 4
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one gdn_decode_kernel launch at this
 # workload, from the ncu capture summarised in profiles/gdn_decode_kernel_config1.md.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1024897792
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1025223168
 
 
 def parse_args():
@@ -353,7 +353,7 @@ def run_b200(args):
                     "d2h_bytes_per_step": D2H_BYTES * world, "ms_per_step": round(e2e_ms / args.steps, 5),
                     "api": "cuda_extension.gdn_decode_forward"},
             "gpu_launches": args.steps,
-            "roofline": {"bound": "hbm", "kernel": "gdn_decode_kernel", "achieved": round(per_gpu, 2),
+            "roofline": {"bound": "hbm", "kernel": "gdn_decode_v8_kernel<8>", "achieved": round(per_gpu, 2),
                          "peak": peak, "unit": "GB/s", "frac": round(per_gpu / peak, 4),
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes": BYTES_PER_STEP,
                          "peak_source": peak_src},

@@ -12,8 +12,10 @@
 // shared memory, no tensor-core work and no second pass. The kernel is bound by
 // HBM bandwidth: 2*64 KiB of state traffic per (b, hv) against ~0.1 MFLOP.
 //
-// Launch shape: one CTA of 8 warps per (b, hv); a warp walks 16 rows, ROWS at a
-// time, so that ROWS independent 128-bit loads per thread are in flight.
+// Launch shape: one CTA of 8 warps per (b, hv); a warp walks 16 rows. The default kernel
+// (gdn_decode_v8_kernel) gives a half-warp one row (16 lanes x 8 floats, 256-bit loads and stores) and
+// keeps 16 rows per warp in flight; gdn_decode_kernel is the 128-bit form (a warp per row, ROWS rows in
+// flight), kept for states that are not 32-byte aligned and as a tuning reference.
 #include "cab_common.cuh"
 
 namespace {
@@ -96,6 +98,87 @@ gdn_decode_kernel(float* __restrict__ state, float* __restrict__ out,
   }
 }
 
+// Variant with 256-bit accesses: a half-warp owns a row (16 lanes x 8 floats), a warp works on PAIRS row
+// pairs at a time. Same arithmetic per element as the kernel above, but the dot products are reduced over
+// 16 lanes (4 shuffle steps for two rows instead of 5 per row), so results can differ in the last bits.
+__device__ __forceinline__ void ld_stream8(const float* p, float (&v)[8]) {
+  asm volatile("ld.global.cs.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+               : "l"(p));
+}
+__device__ __forceinline__ void st_stream8(float* p, const float (&v)[8]) {
+  asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               :
+               : "l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
+}
+
+template <int PAIRS>
+__global__ void __launch_bounds__(kWarpsPerCta * cab::kWarp)
+gdn_decode_v8_kernel(float* __restrict__ state, float* __restrict__ out, const uint4* __restrict__ q,
+                     const uint4* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                     const float* __restrict__ g, const float* __restrict__ beta, int Hq, int Hv, int group) {
+  const int unit = blockIdx.x;
+  const int b = unit / Hv;
+  const int hv = unit - b * Hv;
+  const int qk_unit = b * Hq + hv / group;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int l16 = lane & 15, half = lane >> 4;
+
+  const uint4 kraw = __ldg(k + qk_unit * (kD / 8) + l16);
+  const uint4 qraw = __ldg(q + qk_unit * (kD / 8) + l16);
+  const float kk[8] = {cab::bf16_lo(kraw.x), cab::bf16_hi(kraw.x), cab::bf16_lo(kraw.y), cab::bf16_hi(kraw.y),
+                       cab::bf16_lo(kraw.z), cab::bf16_hi(kraw.z), cab::bf16_lo(kraw.w), cab::bf16_hi(kraw.w)};
+  const float qq[8] = {cab::bf16_lo(qraw.x), cab::bf16_hi(qraw.x), cab::bf16_lo(qraw.y), cab::bf16_hi(qraw.y),
+                       cab::bf16_lo(qraw.z), cab::bf16_hi(qraw.z), cab::bf16_lo(qraw.w), cab::bf16_hi(qraw.w)};
+  float kq = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) kq += kk[i] * qq[i];
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) kq += __shfl_xor_sync(0xffffffffu, kq, off);
+
+  const float alpha = expf(__ldg(g + unit));
+  const float bt = __ldg(beta + unit);
+  const float inv_sqrt_d = 0.08838834764831845f;
+  const int row_base = warp * kRowsPerWarp;
+  float* sbase = state + (size_t)unit * (kD * kD) + l16 * 8;
+  const __nv_bfloat16* vrow = v + (size_t)unit * kD;
+  float* orow = out + (size_t)unit * kD;
+
+#pragma unroll 1
+  for (int it = 0; it < kRowsPerWarp / 2 / PAIRS; ++it) {
+    float s[PAIRS][8];
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) ld_stream8(sbase + (size_t)(row_base + (it * PAIRS + p) * 2 + half) * kD, s[p]);
+    __syncwarp();   // keeps all PAIRS loads in flight (see the kernel above)
+    float uk[PAIRS], uq[PAIRS];
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      uk[p] = 0.f; uq[p] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { uk[p] += s[p][i] * kk[i]; uq[p] += s[p][i] * qq[i]; }
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1)
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) {
+        uk[p] += __shfl_xor_sync(0xffffffffu, uk[p], off);
+        uq[p] += __shfl_xor_sync(0xffffffffu, uq[p], off);
+      }
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      const int row = row_base + (it * PAIRS + p) * 2 + half;
+      const float vi = __bfloat162float(vrow[row]);
+      const float c = bt * (vi - alpha * uk[p]);
+      float t[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) t[i] = alpha * s[p][i] + c * kk[i];
+      st_stream8(sbase + (size_t)row * kD, t);
+      if (l16 == 0) orow[row] = (alpha * uq[p] + c * kq) * inv_sqrt_d;
+    }
+  }
+}
+
 template <int ROWS>
 int launch(float* state, float* out, const cab_bf16* q, const cab_bf16* k, const cab_bf16* v,
            const float* g, const float* beta, int B, int Hq, int Hv, cudaStream_t stream) {
@@ -119,6 +202,20 @@ extern "C" int gdn_decode_launcher(float* state, float* out, const cab_bf16* q, 
   if (!cab::aligned_to(state, 16) || !cab::aligned_to(out, 16) || !cab::aligned_to(q, 8) ||
       !cab::aligned_to(k, 8) || !cab::aligned_to(v, 2))
     return CAB_ERR_MISALIGNED;
+  // config 0 (default) and 3 use 256-bit accesses (half-warp per row); they need a 32-byte aligned state
+  // and 16-byte aligned q/k, otherwise the 128-bit kernel with the same amount in flight takes over.
+  const bool v8_ok = cab::aligned_to(state, 32) && cab::aligned_to(q, 16) && cab::aligned_to(k, 16);
+  if ((config == 3 || config < 1 || config > 4) && v8_ok) {
+    const unsigned grid = static_cast<unsigned>(B) * static_cast<unsigned>(Hv);
+    const uint4* q4 = reinterpret_cast<const uint4*>(q);
+    const uint4* k4 = reinterpret_cast<const uint4*>(k);
+    const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(v);
+    if (config == 3)
+      gdn_decode_v8_kernel<4><<<grid, kWarpsPerCta * cab::kWarp, 0, stream>>>(state, out, q4, k4, vb, g, beta, Hq, Hv, Hv / Hq);
+    else
+      gdn_decode_v8_kernel<8><<<grid, kWarpsPerCta * cab::kWarp, 0, stream>>>(state, out, q4, k4, vb, g, beta, Hq, Hv, Hv / Hq);
+    return cab::launch_status();
+  }
   switch (config) {
     case 1: return launch<4>(state, out, q, k, v, g, beta, B, Hq, Hv, stream);
     case 2: return launch<16>(state, out, q, k, v, g, beta, B, Hq, Hv, stream);

@@ -77,8 +77,12 @@ int axpby_launcher(float* out, const float* a, const float* b, float alpha, int 
 /* v     : bf16 [B, Hv, 128]                                                   */
 /* g     : fp32 [B, Hv]  log-decay (<= 0);   beta : fp32 [B, Hv]               */
 /* Requires Hv % Hq == 0; state and out 16-byte aligned, q/k/v 8-byte aligned. */
-/* config: 0 default (8 rows in flight per warp), 1 -> 4 rows, 2 -> 16 rows.    */
-/* One launch reads and writes each state element exactly once.               */
+/* config: 0 default: 256-bit accesses, a half-warp per state row, 16 rows in    */
+/* flight per warp (needs state 32-byte and q/k 16-byte aligned, else config 4   */
+/* is used); 3: the same with 8 rows in flight; 1 / 4 / 2: 128-bit accesses, a    */
+/* warp per row, 4 / 8 / 16 rows in flight. Configs 1, 2, 4 give identical bits;  */
+/* 0 and 3 reduce the dot products in a different order and agree with them to    */
+/* fp32 rounding. One launch reads and writes each state element exactly once.   */
 /* ------------------------------------------------------------------------- */
 int gdn_decode_launcher(float* state, float* out, const cab_bf16* q, const cab_bf16* k,
                         const cab_bf16* v, const float* g, const float* beta, int B, int Hq,

@@ -31,7 +31,7 @@ def run_capi(dev, S, q, k, v, g, beta, config=0):
     return out, Sd
 
 
-@pytest.mark.parametrize("config", [0, 1, 2])
+@pytest.mark.parametrize("config", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("B,Hq,Hv", [(4, 8, 8), (1, 1, 1), (3, 2, 4), (5, 1, 6), (2, 16, 32)])
 def test_matches_oracle(cuda_device, B, Hq, Hv, config):
     m = load_oracle("gdn", {"CAB_GDN_CONFIG": 0})
@@ -54,14 +54,25 @@ def test_config0_against_committed_fixture(cuda_device):
                what="state sample vs fixture")
 
 
-def test_all_configs_give_identical_bits(cuda_device):
+def test_launch_variants_agree(cuda_device):
     m = load_oracle("gdn", {"CAB_GDN_CONFIG": 0})
     gen = torch.Generator().manual_seed(5)
     S = m.make_state(3, 4, gen)
     step = m.make_step_inputs(3, 2, 4, gen)
-    results = [run_capi(cuda_device, S, *step, config=c) for c in (0, 1, 2)]
+    results = [run_capi(cuda_device, S, *step, config=c) for c in (4, 1, 2)]      # 128-bit variants
     for o, S_new in results[1:]:
         assert torch.equal(o, results[0][0]) and torch.equal(S_new, results[0][1])
+    wide = [run_capi(cuda_device, S, *step, config=c) for c in (0, 3)]            # 256-bit variants
+    assert torch.equal(wide[0][0], wide[1][0]) and torch.equal(wide[0][1], wide[1][1])
+    torch.testing.assert_close(wide[0][1], results[0][1], rtol=1e-5, atol=1e-7)
+    # an unaligned state falls back to the 128-bit kernel
+    from cuda_agent_b200 import capi
+    pad = torch.zeros(S.numel() + 4, device=cuda_device)
+    view = pad[4:].view_as(S)                      # 16-byte but not 32-byte aligned
+    view.copy_(S)
+    out = torch.empty(3, 4, 128, device=cuda_device)
+    capi.gdn_decode(view, out, *[t.to(cuda_device) for t in step], 0)
+    assert torch.equal(view, results[0][1]) and torch.equal(out, results[0][0])
 
 
 def test_multi_step_recurrence_stays_within_tolerance(cuda_device):
