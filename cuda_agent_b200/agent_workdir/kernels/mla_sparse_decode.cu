@@ -427,6 +427,543 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA-pair kernel: 128 query heads of one sequence on a cluster of two CTAs that split the 576
+// columns of the cache rows between them.
+//
+//   CTA r holds value columns [256 r, 256 r + 256) and rotary columns [512 + 32 r, +32) of Q (128
+//   heads) and of every gathered row, so each selected row crosses the L2 -> SM path once per
+//   sequence and a stage of 64 rows takes 36 KB instead of 72 KB: four 64-column tiles in the
+//   128-byte swizzle plus one 32-column tile in the 64-byte swizzle. The 256 value columns of Q live
+//   in tensor memory (the A operand of tcgen05.mma may come from there: lane = head, two bf16 per
+//   32-bit column); only its 32 rotary columns stay in shared memory. That leaves room for four
+//   stages. A stage lands in two parts with a barrier each, so Q.K^T starts on the first part while
+//   the rest of the block is still in flight.
+//   S = Q . K^T is computed as two partial sums over those column ranges, M=128 N=64 (twice the
+//   heads per instruction of the single-CTA kernel at the same cost). Four exchange warps read
+//   their CTA's partial from tensor memory and store it into the other CTA's exchange buffer
+//   through distributed shared memory, one block ahead of the softmax; the softmax warps add what
+//   the other CTA stored to their own partial. Both CTAs hold the same fp32 scores (a sum of two
+//   terms does not depend on their order) and run the same softmax.
+//   O = P . V: each CTA accumulates 128 heads x its 256 of the 512 value columns (the first 256
+//   columns of its slice), M=128 N=256.
+//   Eight softmax warps in two groups that take the blocks in turn; warp w works on the 32 heads of
+//   lane quadrant w % 4, one thread per head.
+// Every wait is bounded; a CTA that gives up still reaches the closing cluster barrier, so its
+// partner's stores never hit shared memory of a CTA that has exited.
+constexpr int kPairHeads = 128;
+constexpr int kPairThreads = 18 * 32;              // 8 softmax, Q.K^T issuer, 4 producer, 4 exchange warps, P.V issuer
+constexpr int kPairStages = 4;
+constexpr int kPairTiles = 2;                      // a stage lands in two parts: value tiles 0,1, then 2,3 and the rotary tile
+constexpr int kPairQRopeBytes = kPairHeads * 64;   // 128 heads x 32 rotary columns
+constexpr int kPairRopeOffset = 4 * kChunkBytes;   // rotary tile of a stage: 64 rows x 64 bytes
+constexpr int kPairStageBytes = kPairRopeOffset + kTok * 64;   // 36864
+constexpr int kPairXBytes = kPairHeads * kTok * 4; // partial scores of the other CTA
+constexpr int kPairPBytes = kPairHeads * 128;      // P: 128 heads x 64 tokens bf16
+constexpr uint32_t kPairColS = 0, kPairColQ = 128, kPairColO = 256;
+
+struct __align__(16) PairControl {
+  uint64_t kv_full[kPairStages][kPairTiles], kv_empty[kPairStages], s_full[2], s_empty[2], p_full, p_empty[2], x_full[2],
+      x_free, o_done;   // p_empty and x_full: one barrier for the even and one for the odd blocks
+  uint64_t duo[4];                   // the two softmax warps of a lane quadrant meet here (64 arrivals)
+  uint32_t tmem_base;
+  int abort_flag;
+  unsigned char valid[kPairStages][kTok];
+  float row_ref[kPairHeads];         // reference maximum of each head (log2 units) as the last block left it
+  float row_sum[2][kPairHeads];      // [softmax group][head], used once at the end
+};
+constexpr int kPairSmemBytes = kPairQRopeBytes + kPairStages * kPairStageBytes + kPairXBytes + kPairPBytes +
+                               (int)sizeof(PairControl) + 1024;
+
+enum { kWaitXFull = 208, kWaitXFree = 209, kWaitDuo = 210 };
+
+// 2^x for x <= 0 (and -inf -> 0) in one special-function instruction; results below 2^-126 become 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Operand descriptor for K-major tiles with rows of 64 bytes in the 64-byte swizzle (16-byte unit u of row r
+// sits at unit u ^ ((r >> 1) & 3)); groups of 8 rows are 512 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)4 << 61);
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]^T: the A operand (128 lanes x 8 columns = 128 x 16 bf16) is read from
+// tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Producer warp of the pair kernel: rows [32 pw, +32) of every second block starting at block `grp`.
+// The block is copied as two cp.async groups (value tiles 0 and 1; value tiles 2, 3 and the rotary tile),
+// each published on its own barrier as soon as it has landed.
+__device__ __forceinline__ void pair_produce(const MlaParams& p, PairControl& ctl, uint8_t* kv_tile, int grp, int pw,
+                                             int lane, int b, int j0, int nb, int len, int rank) {
+  volatile int* abort_flag = &ctl.abort_flag;
+  const int* idx_b = p.idx + (size_t)b * p.topk;
+  const uint8_t* kv_b = reinterpret_cast<const uint8_t*>(p.kv + (size_t)b * p.S * kDqk);
+  const int vbyte0 = rank * 512, rbyte0 = 1024 + rank * 64;
+  // The cache row number of this lane's row is fetched one block early, and the slices of the rows of the
+  // block after next are requested into L2 (kPrefetchAhead blocks of this warp pair = twice as many blocks
+  // of the CTA ahead), so that the copies into shared memory mostly hit L2.
+  constexpr int kPrefetchAhead = 2;
+  auto entry = [&](int j) {
+    const int i = (j0 + j) * kTok + pw * 32 + lane;
+    return (j < nb && i < p.topk) ? __ldg(idx_b + i) : -1;
+  };
+  auto prefetch = [&](int t) {
+    if (t >= 0 && t < len) {     // rows start on 128-byte lines: four lines of value columns, one with the rotary ones
+      const uint8_t* row = kv_b + (size_t)t * (kDqk * 2);
+#pragma unroll
+      for (int l = 0; l < 4; ++l) sm100::prefetch_l2_line(row + vbyte0 + l * 128);
+      sm100::prefetch_l2_line(row + rbyte0);
+    }
+  };
+  for (int a = 1; a <= kPrefetchAhead; ++a) prefetch(entry(grp + 2 * a));
+  // every row number is loaded an iteration before it is used, so that no iteration waits for the load
+  int t_next = entry(grp), t_prefetch = entry(grp + 2 * (kPrefetchAhead + 1));
+  for (int j = grp; j < nb; j += 2) {
+    const int st = j % kPairStages, use = j / kPairStages;
+    const int my_t = t_next, pf_t = t_prefetch;
+    t_next = entry(j + 2);
+    t_prefetch = entry(j + 2 * (kPrefetchAhead + 2));
+    prefetch(pf_t);
+    if (use >= 1 && !sm100::mbar_wait_relaxed(&ctl.kv_empty[st], (use - 1) & 1, abort_flag, p.status, kWaitKvEmpty))
+      break;
+    const uint32_t dst = sm100::smem_u32(kv_tile + st * kPairStageBytes);
+    const bool my_ok = my_t >= 0 && my_t < len;
+    ctl.valid[st][pw * 32 + lane] = my_ok ? 1 : 0;
+    const int my_row = my_ok ? my_t : 0;   // an invalid entry copies row 0: finite data under a zero weight
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int piece = it * 32 + lane;
+        const int rl = piece >> 3, c16 = piece & 7;
+        const int r = pw * 32 + rl;
+        const int t = __shfl_sync(0xffffffffu, my_row, rl);
+        cp_async_16(dst + c * kChunkBytes + r * 128 + ((c16 ^ (r & 7)) << 4),
+                    kv_b + (size_t)t * (kDqk * 2) + vbyte0 + c * 128 + c16 * 16);
+      }
+      if (c == 1) cp_async_commit();
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int piece = it * 32 + lane;
+      const int rl = piece >> 2, c16 = piece & 3;
+      const int r = pw * 32 + rl;
+      const int t = __shfl_sync(0xffffffffu, my_row, rl);
+      cp_async_16(dst + kPairRopeOffset + r * 64 + ((c16 ^ ((r >> 1) & 3)) << 4),
+                  kv_b + (size_t)t * (kDqk * 2) + rbyte0 + c16 * 16);
+    }
+    cp_async_commit();
+    cp_async_wait<1>(); sm100::fence_proxy_async(); sm100::mbar_arrive(&ctl.kv_full[st][0]);
+    cp_async_wait<0>(); sm100::fence_proxy_async(); sm100::mbar_arrive(&ctl.kv_full[st][1]);
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+mla_sparse_decode_pair_kernel(const MlaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_rope = base;                              // this CTA's 32 rotary columns of Q, 128 heads x 64 bytes
+  uint8_t* kv_tile = q_rope + kPairQRopeBytes;         // four stages
+  uint8_t* x_tile = kv_tile + kPairStages * kPairStageBytes;   // float4 [16 column groups][128 heads]
+  uint8_t* p_tile = x_tile + kPairXBytes;
+  PairControl& ctl = *reinterpret_cast<PairControl*>(p_tile + kPairPBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = sm100::cluster_ctarank(), peer = rank ^ 1u;
+  const int head0 = (blockIdx.x >> 1) * kPairHeads, split = blockIdx.y, b = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      for (int c = 0; c < kPairTiles; ++c) sm100::mbar_init(&ctl.kv_full[s][c], 64);
+      sm100::mbar_init(&ctl.kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      sm100::mbar_init(&ctl.s_full[s], 1);
+      sm100::mbar_init(&ctl.s_empty[s], 8);           // 4 softmax + 4 exchange warps read every S
+    }
+    sm100::mbar_init(&ctl.p_full, 4);
+    sm100::mbar_init(&ctl.p_empty[0], 1);
+    sm100::mbar_init(&ctl.p_empty[1], 1);
+    sm100::mbar_init(&ctl.x_full[0], 1);            // one local arrival that posts the byte count per block
+    sm100::mbar_init(&ctl.x_full[1], 1);
+    sm100::mbar_init(&ctl.x_free, 4);
+    for (int s = 0; s < 4; ++s) sm100::mbar_init(&ctl.duo[s], 64);
+    sm100::mbar_init(&ctl.o_done, 1);
+    ctl.abort_flag = 0;
+    sm100::mbar_fence_init();
+    sm100::mbar_arrive_expect_tx(&ctl.x_full[0], kPairXBytes);   // partial scores of blocks 0 and 1 from the other CTA
+    sm100::mbar_arrive_expect_tx(&ctl.x_full[1], kPairXBytes);
+  }
+  if (threadIdx.x < kPairHeads) ctl.row_ref[threadIdx.x] = -INFINITY;
+  if (warp == 8) {
+    sm100::tmem_alloc(&ctl.tmem_base, kTmemCols);
+    sm100::tmem_relinquish();
+  }
+  const uint8_t* q_rows = reinterpret_cast<const uint8_t*>(p.q + ((size_t)b * p.Hh + head0) * kDqk);
+  if (threadIdx.x < kPairHeads * 4) {
+    // this CTA's 32 rotary columns of Q as one tile in the 64-byte swizzle
+    const int r = threadIdx.x >> 2, c16 = threadIdx.x & 3;
+    cp_async_16(sm100::smem_u32(q_rope) + r * 64 + ((c16 ^ ((r >> 1) & 3)) << 4),
+                q_rows + (size_t)r * (kDqk * 2) + 1024 + rank * 64 + c16 * 16);
+    cp_async_commit();
+    cp_async_wait<0>();
+    sm100::fence_proxy_async();
+  }
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  sm100::tc_fence_after_sync();
+  const uint32_t tmem_base = ctl.tmem_base;
+  if (warp < 4) {
+    // the 256 value columns of Q into tensor memory: thread = head = lane, 64 columns (128 bytes) per store
+    const uint4* src = reinterpret_cast<const uint4*>(q_rows + (size_t)(warp * 32 + lane) * (kDqk * 2) + rank * 512);
+    const uint32_t dst = tmem_base + ((uint32_t)(warp * 32) << 16) + kPairColQ;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t w[32];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint4 v = __ldg(src + c * 8 + u);
+        w[4 * u] = v.x; w[4 * u + 1] = v.y; w[4 * u + 2] = v.z; w[4 * u + 3] = v.w;
+      }
+      tmem_st_32x32(dst + c * 32, w);
+    }
+    tmem_st_wait();
+  }
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  sm100::cluster_sync_all();          // both CTAs' barriers exist before anything arrives on them remotely
+  sm100::tc_fence_after_sync();
+  volatile int* abort_flag = &ctl.abort_flag;
+
+  const int blocks_total = (p.topk + kTok - 1) / kTok;
+  const int per_split = (blocks_total + p.nsplit - 1) / p.nsplit;
+  const int j0 = split * per_split;
+  const int nb = max(0, min(blocks_total, j0 + per_split) - j0);
+  const int len = __ldg(p.seq_len + b);
+
+  if (warp >= 13 && warp <= 16) {
+    // ---------------------------------------------------------------- exchange warps (one per lane quadrant)
+    sm100::reg_dec<88>();
+    const int quad = warp & 3;        // a warp reaches the tensor-memory lanes of quadrant warp % 4 only
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t peer_x = sm100::cluster_map(sm100::smem_u32(x_tile), peer);
+    const uint32_t peer_x_full0 = sm100::cluster_map(sm100::smem_u32(&ctl.x_full[0]), peer);
+    const uint32_t peer_x_full1 = sm100::cluster_map(sm100::smem_u32(&ctl.x_full[1]), peer);
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      const int sb = j & 1;
+      if (!sm100::mbar_wait(&ctl.s_full[sb], (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) ok = false;
+      if (!__all_sync(0xffffffffu, ok)) break;
+      sm100::tc_fence_after_sync();
+      uint32_t t0[32], t1[32];
+      sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok, t0);
+      sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok + 32, t1);
+      sm100::tmem_ld_wait();
+      sm100::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&ctl.s_empty[sb]);
+      // the other CTA's buffer is free once its softmax warps have added block j-1
+      if (j >= 1 && !sm100::mbar_wait_cluster(&ctl.x_free, (j - 1) & 1, abort_flag, p.status, kWaitXFree)) ok = false;
+      if (!__all_sync(0xffffffffu, ok)) break;
+      // asynchronous stores that count their bytes on the other CTA's barrier when they land
+      const uint32_t peer_x_full = sb ? peer_x_full1 : peer_x_full0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        sm100::st_async_v4(peer_x + (uint32_t)((i * kPairHeads + row) * 16), peer_x_full, t0[4 * i], t0[4 * i + 1],
+                           t0[4 * i + 2], t0[4 * i + 3]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        sm100::st_async_v4(peer_x + (uint32_t)(((8 + i) * kPairHeads + row) * 16), peer_x_full, t1[4 * i],
+                           t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]);
+    }
+  } else if (warp >= 9 && warp <= 12) {
+    // ---------------------------------------------------------------- producers
+    // Warps 9,10 gather the even blocks, warps 11,12 the odd ones; each warp owns 32 of the block's 64
+    // rows and copies this CTA's slice of them (36 sixteen-byte pieces per row).
+    sm100::reg_dec<56>();
+    const int grp = (warp - 9) >> 1, pw = (warp - 9) & 1;
+    pair_produce(p, ctl, kv_tile, grp, pw, lane, b, j0, nb, len, (int)rank);
+  } else if (warp == 8) {
+    // ---------------------------------------------------------------- Q.K^T issuer
+    // Two issuing threads (this one and the P.V issuer in warp 17) instead of one that polls: each
+    // simply waits for what it needs next, and the tensor core takes their instructions as they come.
+    sm100::reg_dec<56>();
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = sm100::umma_idesc(1 /* bf16 */, kPairHeads, kTok);
+      const uint64_t a_rope = umma_desc_sw64(sm100::smem_u32(q_rope));
+      for (int j = 0; j < nb; ++j) {
+        const int st = j % kPairStages, sb = j & 1;
+        const uint32_t ph = (j / kPairStages) & 1;
+        const uint32_t k_addr = sm100::smem_u32(kv_tile + st * kPairStageBytes);
+        const uint32_t d = tmem_base + kPairColS + sb * kTok;
+        if (!sm100::mbar_wait(&ctl.s_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag, p.status, kWaitSEmpty)) break;
+        bool ok = true;
+#pragma unroll
+        for (int c = 0; c < 4 && ok; ++c) {
+          if ((c & 1) == 0) {
+            if (!sm100::mbar_wait(&ctl.kv_full[st][c >> 1], ph, abort_flag, p.status, kWaitKvFull)) { ok = false; break; }
+            sm100::tc_fence_after_sync();
+          }
+          const uint64_t bd = umma_desc_sw128(k_addr + c * kChunkBytes, 16, 1024);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_f16_ts(d, tmem_base + kPairColQ + c * 32 + k4 * 8, bd + 2 * k4, idesc_qk, (c > 0 || k4 > 0) ? 1u : 0u);
+        }
+        if (!ok) break;
+        const uint64_t bd = umma_desc_sw64(k_addr + kPairRopeOffset);
+#pragma unroll
+        for (int k2 = 0; k2 < 2; ++k2) sm100::umma_f16(d, a_rope + 2 * k2, bd + 2 * k2, idesc_qk, 1u);
+        sm100::umma_commit(&ctl.s_full[sb]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 17) {
+    // ---------------------------------------------------------------- P.V issuer
+    sm100::reg_dec<56>();
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = sm100::umma_idesc(1, kPairHeads, 256) | (1u << 16);   // B is MN-major
+      const uint64_t a = umma_desc_sw128(sm100::smem_u32(p_tile), 16, 1024);
+      bool ok = true;
+      for (int j = 0; j < nb; ++j) {
+        const int st = j % kPairStages;
+        if (!sm100::mbar_wait(&ctl.p_full, j & 1, abort_flag, p.status, kWaitPFull)) { ok = false; break; }
+        sm100::tc_fence_after_sync();
+        const uint64_t bd = umma_desc_sw128(sm100::smem_u32(kv_tile + st * kPairStageBytes), kChunkBytes, 1024);
+#pragma unroll
+        for (int k4 = 0; k4 < kTok / 16; ++k4)
+          sm100::umma_f16(tmem_base + kPairColO, a + 2 * k4, bd + (uint64_t)k4 * (2048 >> 4), idesc_pv,
+                          (j > 0 || k4 > 0) ? 1u : 0u);
+        sm100::umma_commit(&ctl.kv_empty[st]);      // the stage may be refilled
+        sm100::umma_commit(&ctl.p_empty[j & 1]);    // P and O may be touched again
+      }
+      if (ok) sm100::umma_commit(&ctl.o_done);
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue (warps 0..7)
+    // 18 warps leave 96 registers per thread at launch. Registers are handed over inside each SM
+    // sub-partition (warps w, w+4, w+8, ...: two softmax warps, a producer, an exchange warp, and an
+    // issuing warp in sub-partitions 0 and 1): 2 x 120 + 56 + 88 (+ 56) <= 4 (5) x 96.
+    sm100::reg_inc<120>();
+    // Two groups of four warps take the blocks in turn (group 0 the even ones, group 1 the odd ones), one
+    // thread per head with all 64 scores of the block, so that the waits of one block hide behind the
+    // arithmetic of the other. What orders the blocks is the single P tile: P of block j is written after
+    // P.V of block j-1 has finished. At that point the thread reads the row's reference maximum as block
+    // j-1 left it, decides about raising it, and publishes it for block j+1. The exponentials are computed
+    // earlier against the reference the thread could see then, and once more in the rare case that it
+    // changed in between.
+    const int quad = warp & 3, grp = warp >> 2;
+    const int row = quad * 32 + lane;                  // head inside the 128; tensor-memory lane
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t peer_x_free = sm100::cluster_map(sm100::smem_u32(&ctl.x_free), peer);
+    const float4* x_own = reinterpret_cast<const float4*>(x_tile);
+    volatile float* m_shared = ctl.row_ref;
+    float m_loc = -INFINITY, l_part = 0.f;             // this thread's sum is relative to m_loc
+    bool ok = true;
+    for (int j = grp; j < nb; j += 2) {
+      const int sb = j & 1, st = j % kPairStages;
+      if (!sm100::mbar_wait(&ctl.s_full[sb], (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) { ok = false; }
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      sm100::tc_fence_after_sync();
+      uint32_t t[64];
+      {
+        uint32_t (&t0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&t[0]);
+        uint32_t (&t1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&t[32]);
+        sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok, t0);
+        sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok + 32, t1);
+      }
+      sm100::tmem_ld_wait();
+      sm100::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&ctl.s_empty[sb]);
+
+      // Add the other CTA's partial scores, then hand its buffer back. Each group has its own x_full and
+      // p_empty barrier: a waiter by parity has to see every phase of its barrier, and a group sees only
+      // every second block.
+      if (!sm100::mbar_wait(&ctl.x_full[grp], (j >> 1) & 1, abort_flag, p.status, kWaitXFull)) ok = false;
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      if (quad == 0 && lane == 0 && j + 2 < nb) sm100::mbar_arrive_expect_tx(&ctl.x_full[grp], kPairXBytes);   // block j+2
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float4 o = x_own[i * kPairHeads + row];
+        t[4 * i] = __float_as_uint(__uint_as_float(t[4 * i]) + o.x);
+        t[4 * i + 1] = __float_as_uint(__uint_as_float(t[4 * i + 1]) + o.y);
+        t[4 * i + 2] = __float_as_uint(__uint_as_float(t[4 * i + 2]) + o.z);
+        t[4 * i + 3] = __float_as_uint(__uint_as_float(t[4 * i + 3]) + o.w);
+      }
+      // the values are in registers: tell the other CTA that this warp is done with the buffer
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive_cluster_relaxed(peer_x_free);
+
+      const unsigned v_lo = __ballot_sync(0xffffffffu, ctl.valid[st][lane] != 0);
+      const unsigned v_hi = __ballot_sync(0xffffffffu, ctl.valid[st][32 + lane] != 0);
+      if ((v_lo & v_hi) != 0xffffffffu) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (!(((i < 32 ? v_lo : v_hi) >> (i & 31)) & 1u)) t[i] = __float_as_uint(-INFINITY);
+      }
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(t[i]));
+      const float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;   // scale > 0
+
+      // reference after this block, given the reference before it: raised on the first non-empty block
+      // or on a jump of more than 2^8
+      auto next_ref = [&](float before) {
+        if (m_blk == -INFINITY) return before;
+        if (before == -INFINITY || m_blk > before + kRescaleThreshold) return m_blk;
+        return before;
+      };
+      uint32_t packed[32];
+      float psum;
+      auto exponentials = [&](float ref) {
+        const float neg_m = ref == -INFINITY ? 0.f : -ref;   // exp2(-inf) = 0 for masked entries
+        float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(t[i]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(t[i + 1]), p.scale_log2, neg_m));
+          ps4[(i >> 1) & 3] += p0 + p1;
+          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+      };
+      const float m_guess = next_ref(m_shared[row]);   // block j-1 may not have published yet
+      exponentials(m_guess);
+
+      // P, O and the row's reference may be touched only after P.V of block j-1 has finished
+      if (j >= 1 && !sm100::mbar_wait(&ctl.p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitPEmpty))
+        ok = false;
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      sm100::tc_fence_after_sync();
+      const float m_prev = m_shared[row];
+      const float m_new = next_ref(m_prev);
+      if (m_new != m_guess) exponentials(m_new);
+      // O holds sums relative to m_prev
+      const float factor = (m_prev != -INFINITY && m_new != m_prev) ? exp2f(m_prev - m_new) : 1.f;
+      if (__any_sync(0xffffffffu, factor != 1.f)) {
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t o[32];
+          sm100::tmem_ld_32x32(lane_base + kPairColO + c, o);
+          sm100::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st_32x32(lane_base + kPairColO + c, o);
+        }
+        tmem_st_wait();
+      }
+      if (m_loc != m_new) {
+        l_part = m_loc == -INFINITY ? 0.f : l_part * exp2f(m_loc - m_new);
+        m_loc = m_new;
+      }
+      l_part += psum;
+      m_shared[row] = m_new;
+      {
+        uint8_t* prow = p_tile + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
+      sm100::fence_proxy_async();
+      sm100::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&ctl.p_full);
+    }
+
+    // ------------------------------------------------------------ epilogue
+    if (ok && !sm100::mbar_wait(&ctl.o_done, 0, abort_flag, p.status, kWaitODone)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    // both groups are done: bring the two partial row sums to the final reference and add them
+    float l_row = 0.f, m_fin = -INFINITY;
+    if (ok) {
+      sm100::mbar_arrive(&ctl.duo[quad]);
+      if (!sm100::mbar_wait(&ctl.duo[quad], 0, abort_flag, p.status, kWaitDuo)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      m_fin = m_shared[row];
+      ctl.row_sum[grp][row] = (m_loc == -INFINITY) ? 0.f : l_part * exp2f(m_loc - m_fin);
+      sm100::mbar_arrive(&ctl.duo[quad]);
+      if (!sm100::mbar_wait(&ctl.duo[quad], 1, abort_flag, p.status, kWaitDuo)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      l_row = ctl.row_sum[0][row] + ctl.row_sum[1][row];
+    }
+    if (ok) {
+      sm100::tc_fence_after_sync();
+      const int head = head0 + row;
+      const int half = grp;                                // the two warps of a quadrant share the 256 columns
+      const int col0 = (int)rank * 256 + half * 128;
+      const bool live = nb > 0 && l_row > 0.f;
+      if (p.nsplit == 1) {
+        const float inv = live ? 1.f / l_row : 0.f;
+        __nv_bfloat16* dst = p.out + ((size_t)b * p.Hh + head) * kDv + col0;
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          uint32_t o[32];
+          if (nb > 0) { sm100::tmem_ld_32x32(lane_base + kPairColO + half * 128 + c, o); sm100::tmem_ld_wait(); }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float a = live ? __uint_as_float(o[8 * v + 2 * k]) * inv : 0.f;
+              const float bb = live ? __uint_as_float(o[8 * v + 2 * k + 1]) * inv : 0.f;
+              __nv_bfloat162 pk = __floats2bfloat162_rn(a, bb);
+              w[k] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(dst + c + 8 * v) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      } else {
+        const size_t slot = ((size_t)b * p.nsplit + split) * p.Hh + head;
+        float* dst = p.part_o + slot * kDv + col0;
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 32) {
+          uint32_t o[32];
+          if (nb > 0) { sm100::tmem_ld_32x32(lane_base + kPairColO + half * 128 + c, o); sm100::tmem_ld_wait(); }
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            float4 f;
+            f.x = live ? __uint_as_float(o[4 * v + 0]) : 0.f;
+            f.y = live ? __uint_as_float(o[4 * v + 1]) : 0.f;
+            f.z = live ? __uint_as_float(o[4 * v + 2]) : 0.f;
+            f.w = live ? __uint_as_float(o[4 * v + 3]) : 0.f;
+            *reinterpret_cast<float4*>(dst + c + 4 * v) = f;
+          }
+        }
+        if (rank == 0 && half == 0) {
+          p.part_ml[slot * 2 + 0] = m_fin;
+          p.part_ml[slot * 2 + 1] = l_row;
+        }
+      }
+    }
+  }
+
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 8) {
+    sm100::tc_fence_after_sync();
+    sm100::tmem_dealloc(tmem_base, kTmemCols);
+  }
+  sm100::cluster_sync_all();          // nobody leaves while the partner may still store into this CTA
+}
+
 // Merge of the per-split partials: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s.
 __global__ void __launch_bounds__(128)
 mla_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
@@ -479,7 +1016,6 @@ extern "C" int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, cons
                                           const int* seq_len, const int* idx, int B, int Hh, int S, int topk,
                                           float softmax_scale, int nsplit, void* scratch, int* status, int config,
                                           cudaStream_t stream) {
-  (void)config;
   if (B == 0) return CAB_OK;
   if (!out || !q || !kv || !seq_len || !idx) return CAB_ERR_BAD_ARGUMENT;
   if (B < 0 || Hh <= 0 || Hh % kHeads != 0 || S <= 0 || topk <= 0 || nsplit <= 0) return CAB_ERR_BAD_ARGUMENT;
@@ -506,7 +1042,19 @@ extern "C" int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, cons
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   if (status && cudaMemsetAsync(status, 0, sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
-  mla_sparse_decode_kernel<<<dim3(Hh / kHeads, nsplit, B), kThreads, kSmemBytes, stream>>>(p);
+  // config 1 forces the single-CTA kernel (64 heads per CTA); otherwise 128-head groups run on CTA pairs
+  if (config != 1 && Hh % kPairHeads == 0) {
+    static bool pair_configured = false;
+    if (!pair_configured) {
+      if (cudaFuncSetAttribute(mla_sparse_decode_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kPairSmemBytes) != cudaSuccess)
+        return CAB_ERR_LAUNCH;
+      pair_configured = true;
+    }
+    mla_sparse_decode_pair_kernel<<<dim3(2 * (Hh / kPairHeads), nsplit, B), kPairThreads, kPairSmemBytes, stream>>>(p);
+  } else {
+    mla_sparse_decode_kernel<<<dim3(Hh / kHeads, nsplit, B), kThreads, kSmemBytes, stream>>>(p);
+  }
   int rc = cab::launch_status();
   if (rc != CAB_OK || nsplit == 1) return rc;
   mla_combine_kernel<<<B * Hh, 128, 0, stream>>>(p.out, p.part_o, p.part_ml, Hh, nsplit);

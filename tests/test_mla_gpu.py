@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 ATOL = 2e-2
 
 
-def run(dev, q, kv, seq_len, idx, nsplit):
+def run(dev, q, kv, seq_len, idx, nsplit, config=0):
     from cuda_agent_b200 import capi
     B, _, Hh, _ = q.shape
     out = torch.full((B, 1, Hh, 512), float("nan"), dtype=torch.bfloat16, device=dev)
@@ -21,7 +21,7 @@ def run(dev, q, kv, seq_len, idx, nsplit):
     nbytes = capi.mla_scratch_bytes(B, Hh, nsplit)
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev) if nbytes else None
     capi.mla_sparse_decode(out, q.to(dev), kv.to(dev), seq_len.to(dev), idx.to(dev), 192 ** -0.5, nsplit, scratch,
-                           status)
+                           status, config)
     torch.cuda.synchronize()
     assert int(status) == 0, f"bounded wait gave up at code {int(status)}"
     return out.cpu()
@@ -37,27 +37,31 @@ def test_matches_oracle(cuda_device, B, Hh, S, topk, min_len, nsplit):
     idx[0, 0, 3] = -1
     idx[B - 1, 0, topk // 2] = S + 5
     ref = m.Model(B, Hh, S, topk)(q, kv, seq_len, idx)
-    out = run(cuda_device, q, kv, seq_len, idx, nsplit)
-    assert torch.isfinite(out.float()).all()
-    err = float((out.float() - ref.float()).abs().max())
-    assert err <= ATOL, err
+    # config 0: 128-head groups run on CTA pairs; config 1 forces the 64-heads-per-CTA kernel
+    for config in ((0, 1) if Hh % 128 == 0 else (0,)):
+        out = run(cuda_device, q, kv, seq_len, idx, nsplit, config)
+        assert torch.isfinite(out.float()).all()
+        err = float((out.float() - ref.float()).abs().max())
+        assert err <= ATOL, (config, err)
 
 
-def test_edge_cases(cuda_device):
+@pytest.mark.parametrize("HH", [64, 128])
+def test_edge_cases(cuda_device, HH):
     """Nothing valid -> zeros; a single valid entry -> that row; wide score range (lazy rescale path)."""
     m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
     gen = torch.Generator().manual_seed(9)
-    q, kv, seq_len, idx = m.make_inputs(3, 64, 400, 192, 300, gen)
+    q, kv, seq_len, idx = m.make_inputs(3, HH, 400, 192, 300, gen)
     idx[0] = -1                                     # sequence 0: nothing selected
     idx[1] = -1; idx[1, 0, 77] = 5                  # sequence 1: exactly one row
     q[2] = q[2] * 6                                 # sequence 2: scores spread over > 2^8, late maxima
     kv[2, :, :] = kv[2, :, :] * torch.linspace(0.2, 3.0, 400)[:, None].to(torch.bfloat16)
-    ref = m.Model(3, 64, 400, 192)(q, kv, seq_len, idx)
+    ref = m.Model(3, HH, 400, 192)(q, kv, seq_len, idx)
     for nsplit in (1, 3):
         out = run(cuda_device, q, kv, seq_len, idx, nsplit)
         assert torch.all(out[0] == 0)
-        torch.testing.assert_close(out[1, 0].float(), kv[1, 5, :512].float().expand(64, 512), rtol=0, atol=1e-2)
-        assert float((out[2].float() - ref[2].float()).abs().max()) <= 6e-2     # |values| up to ~10 here
+        torch.testing.assert_close(out[1, 0].float(), kv[1, 5, :512].float().expand(HH, 512), rtol=0, atol=1e-2)
+        # |values| reach ~10 here, where one bf16 step is 2^-4: allow one step of the output format
+        torch.testing.assert_close(out[2].float(), ref[2].float(), rtol=2.0 ** -7, atol=ATOL)
 
 
 def test_gather_rows_exact(cuda_device):
