@@ -488,7 +488,7 @@ def run_mla(args):
                 "d2h_bytes_per_step": ho.numel() * 2 * world, "ms_per_step": round(ms_e2e, 5),
                 "api": "cuda_extension.mla_sparse_decode_forward"},
         "gpu_launches": steps * (1 if args.nsplit == 1 else 2),
-        "roofline": {"bound": "hbm", "kernel": "mla_sparse_decode_kernel", "achieved": round(gbs, 1),
+        "roofline": {"bound": "hbm", "kernel": "mla_sparse_decode_pair_kernel", "achieved": round(gbs, 1),
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None,
                      "roofline_time_us": round(t_roof * 1e6, 2), "frac_of_roofline_time": round(t_roof / (ms * 1e-3), 4),
                      "peak_source": "MEASURED_PEAKS.json (hbm_gbs; bf16_tflops for the compute side)"},

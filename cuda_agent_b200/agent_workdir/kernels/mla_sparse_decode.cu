@@ -441,9 +441,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
 //   the rest of the block is still in flight.
 //   S = Q . K^T is computed as two partial sums over those column ranges, M=128 N=64 (twice the
 //   heads per instruction of the single-CTA kernel at the same cost). Four exchange warps read
-//   their CTA's partial from tensor memory and store it into the other CTA's exchange buffer
-//   through distributed shared memory, one block ahead of the softmax; the softmax warps add what
-//   the other CTA stored to their own partial. Both CTAs hold the same fp32 scores (a sum of two
+//   their CTA's partial from tensor memory, store it into the other CTA's exchange buffer through
+//   distributed shared memory, add what the other CTA stored here and write the complete scores
+//   back to tensor memory, ahead of the softmax. Both CTAs hold the same fp32 scores (a sum of two
 //   terms does not depend on their order) and run the same softmax.
 //   O = P . V: each CTA accumulates 128 heads x its 256 of the 512 value columns (the first 256
 //   columns of its slice), M=128 N=256.
@@ -463,8 +463,8 @@ constexpr int kPairPBytes = kPairHeads * 128;      // P: 128 heads x 64 tokens b
 constexpr uint32_t kPairColS = 0, kPairColQ = 128, kPairColO = 256;
 
 struct __align__(16) PairControl {
-  uint64_t kv_full[kPairStages][kPairTiles], kv_empty[kPairStages], s_full[2], s_empty[2], p_full, p_empty[2], x_full[2],
-      x_free, o_done;   // p_empty and x_full: one barrier for the even and one for the odd blocks
+  uint64_t kv_full[kPairStages][kPairTiles], kv_empty[kPairStages], s_full[2], s_ready[2], s_empty[2], p_full, p_empty[2],
+      x_full[2][2], x_free[2], o_done;   // p_empty, x_full: [even / odd blocks]; x_full, x_free: [.. column half]
   uint64_t duo[4];                   // the two softmax warps of a lane quadrant meet here (64 arrivals)
   uint32_t tmem_base;
   int abort_flag;
@@ -503,53 +503,55 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       : "memory");
 }
 
-// Producer warp of the pair kernel: rows [32 pw, +32) of every second block starting at block `grp`.
+// Producer warp `pw` (0..3) of the pair kernel: rows [16 pw, +16) of every block. A warp needs about
+// 100 clk per 16-byte-per-lane cp.async instruction whatever the number of warps copying, so the four
+// warps share each block (18 instructions each) instead of taking blocks in turn (36 each).
 // The block is copied as two cp.async groups (value tiles 0 and 1; value tiles 2, 3 and the rotary tile),
 // each published on its own barrier as soon as it has landed.
-__device__ __forceinline__ void pair_produce(const MlaParams& p, PairControl& ctl, uint8_t* kv_tile, int grp, int pw,
+__device__ __forceinline__ void pair_produce(const MlaParams& p, PairControl& ctl, uint8_t* kv_tile, int pw,
                                              int lane, int b, int j0, int nb, int len, int rank) {
   volatile int* abort_flag = &ctl.abort_flag;
   const int* idx_b = p.idx + (size_t)b * p.topk;
   const uint8_t* kv_b = reinterpret_cast<const uint8_t*>(p.kv + (size_t)b * p.S * kDqk);
   const int vbyte0 = rank * 512, rbyte0 = 1024 + rank * 64;
-  // The cache row number of this lane's row is fetched one block early, and the slices of the rows of the
-  // block after next are requested into L2 (kPrefetchAhead blocks of this warp pair = twice as many blocks
-  // of the CTA ahead), so that the copies into shared memory mostly hit L2.
-  constexpr int kPrefetchAhead = 2;
+  // The cache row number of this lane's row (lanes l and l+16 hold the same one) is fetched one block
+  // early, and the slices of rows further ahead are requested into L2 by lanes 0-15, so that the copies
+  // into shared memory mostly hit L2.
+  constexpr int kPrefetchAhead = 4;
   auto entry = [&](int j) {
-    const int i = (j0 + j) * kTok + pw * 32 + lane;
+    const int i = (j0 + j) * kTok + pw * 16 + (lane & 15);
     return (j < nb && i < p.topk) ? __ldg(idx_b + i) : -1;
   };
   auto prefetch = [&](int t) {
-    if (t >= 0 && t < len) {     // rows start on 128-byte lines: four lines of value columns, one with the rotary ones
+    if (lane < 16 && t >= 0 && t < len) {   // rows start on 128-byte lines: four lines of value columns, one with the rotary ones
       const uint8_t* row = kv_b + (size_t)t * (kDqk * 2);
 #pragma unroll
       for (int l = 0; l < 4; ++l) sm100::prefetch_l2_line(row + vbyte0 + l * 128);
       sm100::prefetch_l2_line(row + rbyte0);
     }
   };
-  for (int a = 1; a <= kPrefetchAhead; ++a) prefetch(entry(grp + 2 * a));
+  for (int a = 1; a <= kPrefetchAhead; ++a) prefetch(entry(a));
   // every row number is loaded an iteration before it is used, so that no iteration waits for the load
-  int t_next = entry(grp), t_prefetch = entry(grp + 2 * (kPrefetchAhead + 1));
-  for (int j = grp; j < nb; j += 2) {
+  int t_next = entry(0), t_prefetch = entry(kPrefetchAhead + 1);
+  for (int j = 0; j < nb; ++j) {
     const int st = j % kPairStages, use = j / kPairStages;
     const int my_t = t_next, pf_t = t_prefetch;
-    t_next = entry(j + 2);
-    t_prefetch = entry(j + 2 * (kPrefetchAhead + 2));
+    t_next = entry(j + 1);
+    t_prefetch = entry(j + kPrefetchAhead + 2);
     prefetch(pf_t);
     if (use >= 1 && !sm100::mbar_wait_relaxed(&ctl.kv_empty[st], (use - 1) & 1, abort_flag, p.status, kWaitKvEmpty))
       break;
     const uint32_t dst = sm100::smem_u32(kv_tile + st * kPairStageBytes);
     const bool my_ok = my_t >= 0 && my_t < len;
-    ctl.valid[st][pw * 32 + lane] = my_ok ? 1 : 0;
+    if (lane < 16) ctl.valid[st][pw * 16 + lane] = my_ok ? 1 : 0;
     const int my_row = my_ok ? my_t : 0;   // an invalid entry copies row 0: finite data under a zero weight
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
+      for (int it = 0; it < 4; ++it) {
         const int piece = it * 32 + lane;
         const int rl = piece >> 3, c16 = piece & 7;
-        const int r = pw * 32 + rl;
+        const int r = pw * 16 + rl;
         const int t = __shfl_sync(0xffffffffu, my_row, rl);
         cp_async_16(dst + c * kChunkBytes + r * 128 + ((c16 ^ (r & 7)) << 4),
                     kv_b + (size_t)t * (kDqk * 2) + vbyte0 + c * 128 + c16 * 16);
@@ -557,10 +559,10 @@ __device__ __forceinline__ void pair_produce(const MlaParams& p, PairControl& ct
       if (c == 1) cp_async_commit();
     }
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
+    for (int it = 0; it < 2; ++it) {
       const int piece = it * 32 + lane;
       const int rl = piece >> 2, c16 = piece & 3;
-      const int r = pw * 32 + rl;
+      const int r = pw * 16 + rl;
       const int t = __shfl_sync(0xffffffffu, my_row, rl);
       cp_async_16(dst + kPairRopeOffset + r * 64 + ((c16 ^ ((r >> 1) & 3)) << 4),
                   kv_b + (size_t)t * (kDqk * 2) + rbyte0 + c16 * 16);
@@ -586,25 +588,26 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
-      for (int c = 0; c < kPairTiles; ++c) sm100::mbar_init(&ctl.kv_full[s][c], 64);
+      for (int c = 0; c < kPairTiles; ++c) sm100::mbar_init(&ctl.kv_full[s][c], 128);
       sm100::mbar_init(&ctl.kv_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       sm100::mbar_init(&ctl.s_full[s], 1);
-      sm100::mbar_init(&ctl.s_empty[s], 8);           // 4 softmax + 4 exchange warps read every S
+      sm100::mbar_init(&ctl.s_ready[s], 4);           // the exchange warps have completed the scores
+      sm100::mbar_init(&ctl.s_empty[s], 4);           // the softmax warps of one group have read them
     }
     sm100::mbar_init(&ctl.p_full, 4);
     sm100::mbar_init(&ctl.p_empty[0], 1);
     sm100::mbar_init(&ctl.p_empty[1], 1);
-    sm100::mbar_init(&ctl.x_full[0], 1);            // one local arrival that posts the byte count per block
-    sm100::mbar_init(&ctl.x_full[1], 1);
-    sm100::mbar_init(&ctl.x_free, 4);
+    for (int s = 0; s < 4; ++s) sm100::mbar_init(&ctl.x_full[s >> 1][s & 1], 1);   // one local arrival posts the bytes
+    sm100::mbar_init(&ctl.x_free[1], 4);
+    sm100::mbar_init(&ctl.x_free[0], 4);
     for (int s = 0; s < 4; ++s) sm100::mbar_init(&ctl.duo[s], 64);
     sm100::mbar_init(&ctl.o_done, 1);
     ctl.abort_flag = 0;
     sm100::mbar_fence_init();
-    sm100::mbar_arrive_expect_tx(&ctl.x_full[0], kPairXBytes);   // partial scores of blocks 0 and 1 from the other CTA
-    sm100::mbar_arrive_expect_tx(&ctl.x_full[1], kPairXBytes);
+    for (int s = 0; s < 4; ++s)   // partial scores of blocks 0 and 1 from the other CTA, in two column halves each
+      sm100::mbar_arrive_expect_tx(&ctl.x_full[s >> 1][s & 1], kPairXBytes / 2);
   }
   if (threadIdx.x < kPairHeads) ctl.row_ref[threadIdx.x] = -INFINITY;
   if (warp == 8) {
@@ -660,8 +663,12 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t peer_x = sm100::cluster_map(sm100::smem_u32(x_tile), peer);
-    const uint32_t peer_x_full0 = sm100::cluster_map(sm100::smem_u32(&ctl.x_full[0]), peer);
-    const uint32_t peer_x_full1 = sm100::cluster_map(sm100::smem_u32(&ctl.x_full[1]), peer);
+    // The exchange buffer is used in two halves (score columns 0-31 and 32-63) with their own barriers,
+    // so that the second half is on its way while the first is added, and the other CTA may refill the
+    // first half while the second is still being read.
+    const uint32_t peer_bar0 = sm100::cluster_map(sm100::smem_u32(&ctl.x_full[0][0]), peer);   // [sb][half]: + 16 sb + 8 half
+    const uint32_t peer_free0 = sm100::cluster_map(sm100::smem_u32(&ctl.x_free[0]), peer);
+    const float4* x_own = reinterpret_cast<const float4*>(x_tile);
     bool ok = true;
     for (int j = 0; j < nb; ++j) {
       const int sb = j & 1;
@@ -672,30 +679,62 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
       sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok, t0);
       sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok + 32, t1);
       sm100::tmem_ld_wait();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        // the other CTA's half buffer is free once its exchange warps have read block j-1 out of it
+        if (j >= 1 && !sm100::mbar_wait_cluster(&ctl.x_free[half], (j - 1) & 1, abort_flag, p.status, kWaitXFree))
+          ok = false;
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        // asynchronous stores that count their bytes on the other CTA's barrier when they land
+        const uint32_t bar = peer_bar0 + 16 * sb + 8 * half;
+        const uint32_t (&t)[32] = half ? t1 : t0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          sm100::st_async_v4(peer_x + (uint32_t)(((half * 8 + i) * kPairHeads + row) * 16), bar, t[4 * i], t[4 * i + 1],
+                             t[4 * i + 2], t[4 * i + 3]);
+      }
+      if (!ok) break;
+      // what the other CTA stored here: add it, hand each half back at once, and write the complete
+      // scores over the partial ones in tensor memory for the softmax warps
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (!sm100::mbar_wait(&ctl.x_full[sb][half], (j >> 1) & 1, abort_flag, p.status, kWaitXFull)) ok = false;
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        if (quad == 0 && lane == 0 && j + 2 < nb)
+          sm100::mbar_arrive_expect_tx(&ctl.x_full[sb][half], kPairXBytes / 2);   // block j+2
+        uint32_t (&t)[32] = half ? t1 : t0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float4 xa[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) xa[i] = x_own[(half * 8 + h * 4 + i) * kPairHeads + row];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t* dst = &t[(h * 4 + i) * 4];
+            dst[0] = __float_as_uint(__uint_as_float(dst[0]) + xa[i].x);
+            dst[1] = __float_as_uint(__uint_as_float(dst[1]) + xa[i].y);
+            dst[2] = __float_as_uint(__uint_as_float(dst[2]) + xa[i].z);
+            dst[3] = __float_as_uint(__uint_as_float(dst[3]) + xa[i].w);
+          }
+        }
+        // every value read from this half has been used: it may be overwritten
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive_cluster_relaxed(peer_free0 + 8 * half);
+      }
+      if (!ok) break;
+      tmem_st_32x32(lane_base + kPairColS + sb * kTok, t0);
+      tmem_st_32x32(lane_base + kPairColS + sb * kTok + 32, t1);
+      tmem_st_wait();
       sm100::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&ctl.s_empty[sb]);
-      // the other CTA's buffer is free once its softmax warps have added block j-1
-      if (j >= 1 && !sm100::mbar_wait_cluster(&ctl.x_free, (j - 1) & 1, abort_flag, p.status, kWaitXFree)) ok = false;
-      if (!__all_sync(0xffffffffu, ok)) break;
-      // asynchronous stores that count their bytes on the other CTA's barrier when they land
-      const uint32_t peer_x_full = sb ? peer_x_full1 : peer_x_full0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        sm100::st_async_v4(peer_x + (uint32_t)((i * kPairHeads + row) * 16), peer_x_full, t0[4 * i], t0[4 * i + 1],
-                           t0[4 * i + 2], t0[4 * i + 3]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        sm100::st_async_v4(peer_x + (uint32_t)(((8 + i) * kPairHeads + row) * 16), peer_x_full, t1[4 * i],
-                           t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]);
+      if (lane == 0) sm100::mbar_arrive(&ctl.s_ready[sb]);
     }
   } else if (warp >= 9 && warp <= 12) {
     // ---------------------------------------------------------------- producers
-    // Warps 9,10 gather the even blocks, warps 11,12 the odd ones; each warp owns 32 of the block's 64
-    // rows and copies this CTA's slice of them (36 sixteen-byte pieces per row).
+    // each warp owns 16 of every block's 64 rows and copies this CTA's slice of them (36 sixteen-byte
+    // pieces per row)
     sm100::reg_dec<56>();
-    const int grp = (warp - 9) >> 1, pw = (warp - 9) & 1;
-    pair_produce(p, ctl, kv_tile, grp, pw, lane, b, j0, nb, len, (int)rank);
+    pair_produce(p, ctl, kv_tile, warp - 9, lane, b, j0, nb, len, (int)rank);
   } else if (warp == 8) {
     // ---------------------------------------------------------------- Q.K^T issuer
     // Two issuing threads (this one and the P.V issuer in warp 17) instead of one that polls: each
@@ -768,14 +807,12 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
     const int quad = warp & 3, grp = warp >> 2;
     const int row = quad * 32 + lane;                  // head inside the 128; tensor-memory lane
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const uint32_t peer_x_free = sm100::cluster_map(sm100::smem_u32(&ctl.x_free), peer);
-    const float4* x_own = reinterpret_cast<const float4*>(x_tile);
     volatile float* m_shared = ctl.row_ref;
     float m_loc = -INFINITY, l_part = 0.f;             // this thread's sum is relative to m_loc
     bool ok = true;
     for (int j = grp; j < nb; j += 2) {
       const int sb = j & 1, st = j % kPairStages;
-      if (!sm100::mbar_wait(&ctl.s_full[sb], (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) { ok = false; }
+      if (!sm100::mbar_wait(&ctl.s_ready[sb], (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) { ok = false; }
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       sm100::tc_fence_after_sync();
       uint32_t t[64];
@@ -789,24 +826,6 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
       sm100::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&ctl.s_empty[sb]);
-
-      // Add the other CTA's partial scores, then hand its buffer back. Each group has its own x_full and
-      // p_empty barrier: a waiter by parity has to see every phase of its barrier, and a group sees only
-      // every second block.
-      if (!sm100::mbar_wait(&ctl.x_full[grp], (j >> 1) & 1, abort_flag, p.status, kWaitXFull)) ok = false;
-      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      if (quad == 0 && lane == 0 && j + 2 < nb) sm100::mbar_arrive_expect_tx(&ctl.x_full[grp], kPairXBytes);   // block j+2
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float4 o = x_own[i * kPairHeads + row];
-        t[4 * i] = __float_as_uint(__uint_as_float(t[4 * i]) + o.x);
-        t[4 * i + 1] = __float_as_uint(__uint_as_float(t[4 * i + 1]) + o.y);
-        t[4 * i + 2] = __float_as_uint(__uint_as_float(t[4 * i + 2]) + o.z);
-        t[4 * i + 3] = __float_as_uint(__uint_as_float(t[4 * i + 3]) + o.w);
-      }
-      // the values are in registers: tell the other CTA that this warp is done with the buffer
-      __syncwarp();
-      if (lane == 0) sm100::mbar_arrive_cluster_relaxed(peer_x_free);
 
       const unsigned v_lo = __ballot_sync(0xffffffffu, ctl.valid[st][lane] != 0);
       const unsigned v_hi = __ballot_sync(0xffffffffu, ctl.valid[st][32 + lane] != 0);
