@@ -212,10 +212,12 @@ int moe_grouped_gemm_fp8_launcher(int mode, void* out, float* out_scales_t, cons
 /*                                   entry counts iff 0 <= idx < seq_len[b]      */
 /*   out      bf16 [B, 1, Hh, 512] = softmax(q . kv[idx]^T * softmax_scale)      */
 /*                                   . kv[idx][:, :512]; zeros if nothing valid  */
-/* nsplit > 1 divides the topk entries over nsplit CTAs per (sequence, 64 heads) */
-/* and merges their partial results; it needs `scratch`, device memory of        */
+/* nsplit > 1 divides the topk entries over nsplit parts per (sequence, head     */
+/* group) and merges their partial results; it needs `scratch`, device memory of        */
 /* mla_sparse_decode_scratch_bytes(B, Hh, nsplit) bytes (16-byte aligned,         */
 /* contents irrelevant on entry). status: as for moe_grouped_gemm_fp8_launcher.   */
+/* config: 0 = head groups of 128 run on pairs of CTAs when Hh % 128 == 0 (the    */
+/* pairs split the 576 columns), else 64 heads per CTA; 1 = always 64 heads per CTA. */
 /* ------------------------------------------------------------------------- */
 size_t mla_sparse_decode_scratch_bytes(int B, int Hh, int nsplit);
 int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv, const int* seq_len,
