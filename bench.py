@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--config", type=int, default=0, help="launcher variant passed to the op")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="gdn: also time the loop recorded as CUDA graphs (extra key \"cuda_graph\")")
     ap.add_argument("--workload", choices=["gdn", "moe", "mla", "moe_ep"], default="gdn",
                     help="gdn = the headline line; moe = FP8 MoE layer (4096 tokens, 64 experts, top-6); "
                          "mla = top-2048 sparse MLA decode (64 sequences, 128 heads)")
@@ -271,6 +273,23 @@ def run_b200(args):
     ms_total = ev0.elapsed_time(ev1)
     assert bool(torch.isfinite(out).all()), "non-finite decode output"
 
+    # ---- the same loop recorded as CUDA graphs of N_DISTINCT_STEPS launches each (reported beside the headline)
+    graph_ms = None
+    if args.graph:
+        from cuda_agent_b200.graphs import GdnDecodeGraph
+        gdn_graph = GdnDecodeGraph(state, out, q, k, v, g, beta, args.config)
+        replays = max(1, args.steps // N_DISTINCT_STEPS)
+        gdn_graph.replay()
+        barrier()
+        w0 = time.monotonic()
+        ev0.record(stream)
+        for _ in range(replays):
+            gdn_graph.replay()
+        ev1.record(stream)
+        barrier()
+        windows.append((w0, time.monotonic()))
+        graph_ms = ev0.elapsed_time(ev1) / (replays * N_DISTINCT_STEPS)
+
     # ---- end to end through the extension op, host buffers in, host buffer out
     pin = lambda t: t.cpu().pin_memory()
     hq, hk, hv_, hg, hb = pin(q), pin(k), pin(v), pin(g), pin(beta)
@@ -359,6 +378,9 @@ def run_b200(args):
                          "peak_source": peak_src},
             "clocks": sampler.summary(windows),
         }
+        if graph_ms is not None:
+            line["cuda_graph"] = {"ms_per_step": round(graph_ms, 5), "value": round(BYTES_PER_STEP / graph_ms / 1e6, 2),
+                                  "unit": "GB/s per GPU", "launches_per_graph": N_DISTINCT_STEPS}
         if world == 1 and not args.no_cpu_baseline:
             gbs, dt, sample, threads = time_oracle_cpu(n_steps=20, n_warmup=1, budget_s=15.0)
             line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",

@@ -48,14 +48,14 @@ struct __align__(16) Control {
 constexpr int kSmemBytes = 3 * kTileBytes + kPBytes + (int)sizeof(Control) + 1024;
 
 struct MlaParams {
-  const __nv_bfloat16* q;      // [B, 1, Hh, 576]
+  const __nv_bfloat16* q;      // [B, Sq, Hh, 576]
   const __nv_bfloat16* kv;     // [B, S, 576]
-  const int* seq_len;          // [B]
-  const int* idx;              // [B, 1, topk]
-  __nv_bfloat16* out;          // [B, 1, Hh, 512]                 (nsplit == 1)
-  float* part_o;               // [B, nsplit, Hh, 512] unnormalised (nsplit > 1)
-  float* part_ml;              // [B, nsplit, Hh, 2]  (reference max in log2 units, sum)
-  int Hh, S, topk, nsplit;
+  const int* seq_len;          // [B, Sq]
+  const int* idx;              // [B, Sq, topk]
+  __nv_bfloat16* out;          // [B, Sq, Hh, 512]                (nsplit == 1)
+  float* part_o;               // [B*Sq, nsplit, Hh, 512] unnormalised (nsplit > 1)
+  float* part_ml;              // [B*Sq, nsplit, Hh, 2]  (reference max in log2 units, sum)
+  int Hh, S, topk, nsplit, Sq; // Sq query tokens per sequence share its cache rows
   float scale_log2;            // softmax scale * log2(e)
   int* status;
 };
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
     // ---------------------------------------------------------------- producers
     const int ptid = threadIdx.x - 5 * 32;
     const int* idx_b = p.idx + (size_t)b * p.topk;
-    const __nv_bfloat16* kv_b = p.kv + (size_t)b * p.S * kDqk;
+    const __nv_bfloat16* kv_b = p.kv + (size_t)(b / p.Sq) * p.S * kDqk;   // b counts (sequence, query token) pairs
     // Iteration j: publish block j-1 as soon as it has landed (nothing newer is in flight yet), then
     // wait for the stage of block j to be released by P.V of block j-2 and start its copies. Block j is
     // in flight while block j-1 is computed.
@@ -512,7 +512,7 @@ __device__ __forceinline__ void pair_produce(const MlaParams& p, PairControl& ct
                                              int lane, int b, int j0, int nb, int len, int rank) {
   volatile int* abort_flag = &ctl.abort_flag;
   const int* idx_b = p.idx + (size_t)b * p.topk;
-  const uint8_t* kv_b = reinterpret_cast<const uint8_t*>(p.kv + (size_t)b * p.S * kDqk);
+  const uint8_t* kv_b = reinterpret_cast<const uint8_t*>(p.kv + (size_t)(b / p.Sq) * p.S * kDqk);   // b: (sequence, query token)
   const int vbyte0 = rank * 512, rbyte0 = 1024 + rank * 64;
   // The cache row number of this lane's row (lanes l and l+16 hold the same one) is fetched one block
   // early, and the slices of rows further ahead are requested into L2 by lanes 0-15, so that the copies
@@ -1031,11 +1031,14 @@ extern "C" size_t mla_sparse_decode_scratch_bytes(int B, int Hh, int nsplit) {
   return (size_t)B * nsplit * Hh * (kDv + 2) * sizeof(float);
 }
 
-extern "C" int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv,
-                                          const int* seq_len, const int* idx, int B, int Hh, int S, int topk,
-                                          float softmax_scale, int nsplit, void* scratch, int* status, int config,
-                                          cudaStream_t stream) {
-  if (B == 0) return CAB_OK;
+extern "C" int mla_sparse_decode_multi_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv,
+                                                const int* seq_len, const int* idx, int B, int Sq, int Hh, int S,
+                                                int topk, float softmax_scale, int nsplit, void* scratch, int* status,
+                                                int config, cudaStream_t stream) {
+  if (B == 0 || Sq == 0) return CAB_OK;
+  if (B < 0 || Sq < 0) return CAB_ERR_BAD_ARGUMENT;
+  if ((long long)B * Sq > 65535) return CAB_ERR_TOO_LARGE;
+  B *= Sq;          // from here on B counts (sequence, query token) pairs; only the cache is indexed per sequence
   if (!out || !q || !kv || !seq_len || !idx) return CAB_ERR_BAD_ARGUMENT;
   if (B < 0 || Hh <= 0 || Hh % kHeads != 0 || S <= 0 || topk <= 0 || nsplit <= 0) return CAB_ERR_BAD_ARGUMENT;
   if (nsplit > 1 && !scratch) return CAB_ERR_BAD_ARGUMENT;
@@ -1057,7 +1060,7 @@ extern "C" int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, cons
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.part_o = static_cast<float*>(scratch);
   p.part_ml = p.part_o ? p.part_o + (size_t)B * nsplit * Hh * kDv : nullptr;
-  p.Hh = Hh; p.S = S; p.topk = topk; p.nsplit = nsplit;
+  p.Hh = Hh; p.S = S; p.topk = topk; p.nsplit = nsplit; p.Sq = Sq;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   if (status && cudaMemsetAsync(status, 0, sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
@@ -1078,6 +1081,14 @@ extern "C" int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, cons
   if (rc != CAB_OK || nsplit == 1) return rc;
   mla_combine_kernel<<<B * Hh, 128, 0, stream>>>(p.out, p.part_o, p.part_ml, Hh, nsplit);
   return cab::launch_status();
+}
+
+extern "C" int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv,
+                                          const int* seq_len, const int* idx, int B, int Hh, int S, int topk,
+                                          float softmax_scale, int nsplit, void* scratch, int* status, int config,
+                                          cudaStream_t stream) {
+  return mla_sparse_decode_multi_launcher(out, q, kv, seq_len, idx, B, 1, Hh, S, topk, softmax_scale, nsplit, scratch,
+                                          status, config, stream);
 }
 
 extern "C" int mla_gather_rows_launcher(cab_bf16* rows, const cab_bf16* kv, const int* seq_len, const int* idx,

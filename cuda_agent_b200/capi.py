@@ -33,6 +33,7 @@ SIGNATURES = {
     "moe_combine_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p]),
     "mla_sparse_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "mla_sparse_decode_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "mla_sparse_decode_multi_launcher": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "mla_sparse_decode_noalloc_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p, c_int, c_void_p]),
     "mla_gather_rows_launcher": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p]),
     "moe_grouped_gemm_fp8_launcher": (c_int, [c_int] + [c_void_p] * 8 + [c_int] * 6 + [c_void_p, c_int, c_void_p]),
@@ -182,6 +183,17 @@ def mla_sparse_decode(out, q, kv, seq_len, idx, softmax_scale: float, nsplit: in
     _check("mla_sparse_decode_launcher",
            lib().mla_sparse_decode_launcher(_p(out), _p(q), _p(kv), _p(seq_len), _p(idx), B, Hh, S, topk,
                                             softmax_scale, nsplit, _opt(scratch), _opt(status), config, _stream()))
+
+
+def mla_sparse_decode_multi(out, q, kv, seq_len, idx, softmax_scale: float, nsplit: int = 1, scratch=None,
+                            status=None, config: int = 0) -> None:
+    """q [B, Sq, Hh, 576], seq_len [B, Sq], idx [B, Sq, topk], out [B, Sq, Hh, 512]: Sq query tokens per sequence."""
+    B, Sq, Hh, _ = q.shape
+    S, topk = kv.shape[1], idx.shape[-1]
+    _check("mla_sparse_decode_multi_launcher",
+           lib().mla_sparse_decode_multi_launcher(_p(out), _p(q), _p(kv), _p(seq_len), _p(idx), B, Sq, Hh, S, topk,
+                                                  softmax_scale, nsplit, _opt(scratch), _opt(status), config,
+                                                  _stream()))
 
 
 def mla_scratch_bytes(B: int, Hh: int, nsplit: int) -> int:

@@ -224,6 +224,16 @@ int mla_sparse_decode_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16*
                                const int* idx, int B, int Hh, int S, int topk, float softmax_scale,
                                int nsplit, void* scratch, int* status, int config, cab_stream_t stream);
 
+/* Several query tokens per sequence (speculative / multi-token decode): the Sq   */
+/* tokens of sequence b share its cache rows, each with its own selection and its */
+/* own valid length (e.g. seq_len[b, s] = cached tokens visible to token s).       */
+/*   q [B, Sq, Hh, 576], seq_len int32 [B, Sq], idx int32 [B, Sq, topk],           */
+/*   out [B, Sq, Hh, 512]; scratch: mla_sparse_decode_scratch_bytes(B * Sq, ...).  */
+/* B * Sq <= 65535. mla_sparse_decode_launcher is the Sq = 1 case.                 */
+int mla_sparse_decode_multi_launcher(cab_bf16* out, const cab_bf16* q, const cab_bf16* kv, const int* seq_len,
+                                     const int* idx, int B, int Sq, int Hh, int S, int topk, float softmax_scale,
+                                     int nsplit, void* scratch, int* status, int config, cab_stream_t stream);
+
 /* Split decode that allocates nothing. No counterpart in the reference.          */
 /* Same arguments and result as mla_sparse_decode_launcher, without the scratch    */
 /* pointer: the split partials go to a fixed array of                               */

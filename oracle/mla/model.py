@@ -16,6 +16,9 @@ Absorbed multi-head latent attention, one new token per sequence:
   p        = softmax over the VALID entries      fp32
   out      = p . kv[b, idx][:, :512]             fp32 -> bf16   [B, 1, Hh, 512]
   a query with no valid entry yields zeros.
+Several query tokens per sequence (speculative / multi-token decode): q [B, Sq, Hh, 576],
+idx [B, Sq, topk], seq_len [B] or [B, Sq]; every token is the one-token operator on the
+shared cache with its own selection and valid length.
 
 ``gather_rows`` is the index-validation + row-gather step on its own (invalid
 entries give zero rows); it is compared bit for bit.
@@ -54,21 +57,32 @@ def gather_rows(kv: torch.Tensor, idx: torch.Tensor, seq_len: torch.Tensor) -> t
 
 
 class Model(nn.Module):
-    """forward(q, kv, seq_len, idx) -> out bf16 [B, 1, Hh, 512]."""
+    """forward(q, kv, seq_len, idx) -> out bf16 [B, Sq, Hh, 512].
+
+    Sq = q.shape[1] query tokens per sequence (1 in the configs): token s of sequence b uses
+    idx[b, s] and the valid length seq_len[b, s] (a [B] seq_len applies to every token)."""
 
     def __init__(self, B: int, Hh: int, S: int, topk: int) -> None:
         super().__init__()
         self.B, self.Hh, self.S, self.topk = B, Hh, S, topk
 
-    def forward(self, q, kv, seq_len, idx):
+    @staticmethod
+    def one_token(q, kv, seq_len, idx):
+        """q [B, Hh, 576], seq_len [B], idx [B, 1, topk] -> fp32 [B, Hh, 512]."""
         ok = valid_mask(idx, seq_len)                                   # [B, topk]
         rows = gather_rows(kv, idx, seq_len).float()                    # [B, topk, 576]
-        scores = torch.einsum("bhd,btd->bht", q[:, 0].float(), rows) * SCALE
+        scores = torch.einsum("bhd,btd->bht", q.float(), rows) * SCALE
         scores = scores.masked_fill(~ok[:, None, :], float("-inf"))
         p = torch.softmax(scores, dim=-1)
         p = torch.nan_to_num(p, nan=0.0)                                # rows with no valid entry
-        out = torch.einsum("bht,btd->bhd", p, rows[..., :D_V])
-        return out.to(torch.bfloat16)[:, None]
+        return torch.einsum("bht,btd->bhd", p, rows[..., :D_V])
+
+    def forward(self, q, kv, seq_len, idx):
+        outs = []
+        for s in range(q.shape[1]):
+            lens = seq_len if seq_len.dim() == 1 else seq_len[:, s]
+            outs.append(self.one_token(q[:, s], kv, lens, idx[:, s:s + 1]))
+        return torch.stack(outs, dim=1).to(torch.bfloat16)
 
 
 _GEN = None

@@ -181,3 +181,33 @@ def test_axpby_smoke_op(cuda_device):
         out = torch.empty_like(a)
         capi.axpby(out[1:], a[1:], b[1:], -0.5)  # misaligned views take the scalar path
         torch.testing.assert_close(out[1:], -0.5 * a[1:] + b[1:], rtol=1e-6, atol=1e-6)
+
+
+def test_decode_loop_as_cuda_graph(cuda_device, built_libs):
+    """Eight steps recorded as one CUDA graph leave the same state and outputs as eight separate launches."""
+    from cuda_agent_b200 import capi
+    from cuda_agent_b200.graphs import GdnDecodeGraph
+    gen = torch.Generator().manual_seed(5)
+    B, Hq, Hv, steps = 4, 8, 8, 8
+    state0 = (torch.randn(B, Hv, 128, 128, generator=gen) * 0.02).to(cuda_device)
+    def unit(x):
+        return (x / x.norm(dim=-1, keepdim=True)).to(torch.bfloat16)
+    q = unit(torch.randn(steps, B, Hq, 128, generator=gen)).to(cuda_device)
+    k = unit(torch.randn(steps, B, Hq, 128, generator=gen)).to(cuda_device)
+    v = torch.randn(steps, B, Hv, 128, generator=gen).to(torch.bfloat16).to(cuda_device)
+    g = (-torch.nn.functional.softplus(torch.randn(steps, B, Hv, generator=gen))).to(cuda_device)
+    beta = torch.sigmoid(torch.randn(steps, B, Hv, generator=gen)).to(cuda_device)
+    ref_state, ref_out = state0.clone(), torch.empty(steps, B, Hv, 128, device=cuda_device)
+    for s in range(steps):
+        capi.gdn_decode(ref_state, ref_out[s], q[s], k[s], v[s], g[s], beta[s])
+    state, out = state0.clone(), torch.zeros(steps, B, Hv, 128, device=cuda_device)
+    graph = GdnDecodeGraph(state, out, q, k, v, g, beta)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(state, ref_state) and torch.equal(out, ref_out)
+    # a second replay continues from the updated state, like eight more launches
+    for s in range(steps):
+        capi.gdn_decode(ref_state, ref_out[s], q[s], k[s], v[s], g[s], beta[s])
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(state, ref_state) and torch.equal(out, ref_out)

@@ -104,3 +104,39 @@ def test_config2_sampled_batches(cuda_device):
     for nsplit in (1, 4):
         out = run(cuda_device, q, kv, seq_len, idx, nsplit)
         assert float((out.float() - ref.float()).abs().max()) <= ATOL
+
+
+@pytest.mark.parametrize("Hh,nsplit", [(64, 1), (64, 2), (128, 1), (128, 3)])
+def test_several_query_tokens_per_sequence(cuda_device, built_libs, Hh, nsplit):
+    """Sq = 3 tokens per sequence share the cache rows; each has its own selection and valid length."""
+    from cuda_agent_b200 import capi
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    gen = torch.Generator().manual_seed(31 + Hh)
+    B, Sq, S, topk = 3, 3, 700, 200
+    _, kv, base_len, _ = m.make_inputs(B, Hh, S, topk, 300, gen)
+    base_len = torch.clamp(base_len, max=S - Sq)
+    q = torch.randn(B, Sq, Hh, 576, generator=gen).to(torch.bfloat16)
+    seq_len = (base_len[:, None] + torch.arange(1, Sq + 1, dtype=torch.int32)[None, :]).contiguous()
+    idx = torch.stack([torch.stack([torch.randperm(int(seq_len[b, s]) + 20, generator=gen)[:topk].to(torch.int32)
+                                    for s in range(Sq)]) for b in range(B)])      # a few entries beyond the length
+    idx[0, 1, :5] = -1
+    ref = m.Model(B, Hh, S, topk)(q, kv, seq_len, idx)
+    out = torch.full((B, Sq, Hh, 512), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    status = torch.ones(1, dtype=torch.int32, device=cuda_device)
+    nbytes = capi.mla_scratch_bytes(B * Sq, Hh, nsplit)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=cuda_device) if nbytes else None
+    capi.mla_sparse_decode_multi(out, q.to(cuda_device), kv.to(cuda_device), seq_len.to(cuda_device),
+                                 idx.to(cuda_device), 192 ** -0.5, nsplit, scratch, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    assert float((out.cpu().float() - ref.float()).abs().max()) <= ATOL
+    # the extension op takes the same shapes; a [B] seq_len is applied to every token
+    import cuda_agent_b200
+    ext = cuda_agent_b200.load_extension()
+    out2 = ext.mla_sparse_decode_forward(q.to(cuda_device), kv.to(cuda_device), seq_len.to(cuda_device),
+                                         idx.to(cuda_device), 192 ** -0.5, nsplit, True, 0)
+    assert torch.equal(out2, out)
+    ref1 = m.Model(B, Hh, S, topk)(q, kv, base_len, idx)
+    out3 = ext.mla_sparse_decode_forward(q.to(cuda_device), kv.to(cuda_device), base_len.to(cuda_device),
+                                         idx.to(cuda_device), 192 ** -0.5, 0, True, 0)
+    assert float((out3.cpu().float() - ref1.float()).abs().max()) <= ATOL

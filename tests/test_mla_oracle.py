@@ -67,3 +67,23 @@ def test_inputs_follow_the_stated_distributions():
         assert len(set(chosen.tolist())) == len(chosen)                 # sampled without replacement
         assert int(chosen.max()) < int(seq_len[b])
         assert len(chosen) == min(64, int(seq_len[b]))
+
+
+def test_several_query_tokens_per_sequence():
+    """Sq > 1: every token is the one-token operator on the shared cache with its own selection and length."""
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    gen = torch.Generator().manual_seed(77)
+    B, Sq, Hh, S, topk = 2, 3, 4, 90, 32
+    _, kv, _, _ = m.make_inputs(B, Hh, S, topk, 40, gen)
+    q = torch.randn(B, Sq, Hh, 576, generator=gen).to(torch.bfloat16)
+    seq_len = torch.tensor([[50, 51, 52], [88, 89, 90]], dtype=torch.int32)
+    idx = torch.randint(-2, S + 3, (B, Sq, topk), generator=gen, dtype=torch.int32)
+    out = m.Model(B, Hh, S, topk)(q, kv, seq_len, idx)
+    assert out.shape == (B, Sq, Hh, 512)
+    for s in range(Sq):
+        ref = mla_f64(q[:, s:s + 1], kv, seq_len[:, s], idx[:, s:s + 1])
+        assert np.abs(out[:, s:s + 1].double().numpy() - ref).max() < 0.01 * np.abs(ref).max() + 4e-3
+    # a [B] seq_len applies to every token of the sequence
+    out1 = m.Model(B, Hh, S, topk)(q, kv, seq_len[:, 0].contiguous(), idx)
+    ref = mla_f64(q[:, 2:3], kv, seq_len[:, 0], idx[:, 2:3])
+    assert np.abs(out1[:, 2:3].double().numpy() - ref).max() < 0.01 * np.abs(ref).max() + 4e-3
