@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--config", type=int, default=0, help="launcher variant passed to the op")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-dedup", action="store_true",
+                    help="moe_ep: send one row per (token, expert) instead of one per (token, destination rank)")
     ap.add_argument("--graph", action="store_true",
                     help="gdn: also time the loop recorded as CUDA graphs (extra key \"cuda_graph\")")
     ap.add_argument("--workload", choices=["gdn", "moe", "mla", "moe_ep"], default="gdn",
@@ -533,7 +535,8 @@ def run_moe_ep(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    wl = MoeEpWorkload(dev, rank, world, micro_batches=args.micro_batches, gemm_ctas=args.config)
+    wl = MoeEpWorkload(dev, rank, world, micro_batches=args.micro_batches, gemm_ctas=args.config,
+                       dedup=False if args.no_dedup else None)
     steps, warmup = min(args.steps, 30), max(3, min(args.warmup, 5))
 
     def barrier():

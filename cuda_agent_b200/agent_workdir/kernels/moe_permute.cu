@@ -208,7 +208,7 @@ moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int
 
 // ------------------------------------------------------------------ combine
 // out[t] = sum over slots (ascending) of w[t,slot] * y[dst_row[t*k+slot]] (+ extra[t]),
-// fp32 accumulate, bf16 result. One CTA per token, 16-byte accesses.
+// fp32 accumulate, bf16 result; slots with a negative row are skipped. One CTA per token, 16-byte accesses.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ y,
                    const int* __restrict__ dst_row, const float* __restrict__ w,
@@ -224,6 +224,7 @@ moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
   for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < k; ++s) {
+      if (rows[s] < 0) continue;          // an empty slot (a copy whose experts use fewer than k slots on this rank)
       const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[s] * H + col));
       const float ws = wts[s];
       acc[0] = fmaf(ws, cab::bf16_lo(raw.x), acc[0]); acc[1] = fmaf(ws, cab::bf16_hi(raw.x), acc[1]);

@@ -70,7 +70,7 @@ class MoeEpWorkload:
     """DeepSeek-V3-shaped expert-parallel layer: T tokens per GPU, H 7168, I 2048, 256 routed experts in
     blocks of 256/N per rank, top-8 sigmoid routing with 8 groups / top-4, one shared expert."""
 
-    def __init__(self, dev, rank, world, T=8192, H=7168, I=2048, E=256, k=8, seed=1238, micro_batches=None,
+    def __init__(self, dev, rank, world, T=8192, H=7168, I=2048, E=256, k=8, seed=1238, micro_batches=None, dedup=None,
                  gemm_ctas=0):
         from .ep import CudaOps
         self.T, self.H, self.I, self.E, self.k, self.world = T, H, I, E, k, world
@@ -92,12 +92,13 @@ class MoeEpWorkload:
         self.ops = CudaOps(router_w, router_bias, w13_q, w13_s, w2_q, w2_s, (s13[0], s13[1], s2[0], s2[1]), k=k,
                            routing=1, n_group=8, topk_group=4, scaling=1.0, num_experts=E, gemm_ctas=gemm_ctas)
         self.micro_batches = micro_batches if micro_batches is not None else 1
+        self.dedup = dedup
         self.flops_per_gpu = 6 * T * k * H * I + 6 * T * H * I          # routed + shared expert GEMMs
 
     def step(self, x=None):
         from .ep import ep_moe_forward
         return ep_moe_forward(self.x if x is None else x, self.ops, self.world,
-                              micro_batches=self.micro_batches)
+                              micro_batches=self.micro_batches, dedup=self.dedup)
 
 
 class MlaWorkload:

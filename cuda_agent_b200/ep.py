@@ -13,9 +13,14 @@ Data path of one layer call on rank r (T local tokens, k experts per token):
   return           all-to-all of the bf16 result rows, split sizes reversed               (NCCL)
   combine          weighted sum per token in slot order (+ shared expert)                 (kernel)
 
-An entry travels once per (token, slot); merging the slots of one token that go to the same rank is a
-later step. The split sizes are needed on the host, so the counts exchange ends in one device-to-host
-copy per call.
+That is `ep_moe_forward(..., dedup=False)`: an entry travels once per (token, slot). With more than one
+rank the default is the merged form (`_ep_dedup`): a token travels ONCE to every rank that holds at least
+one of its experts (with group-limited routing at most `topk_group` ranks instead of k entries), together
+with a side band of k (local expert, weight) slots; the receiving rank expands the copies into its padded
+row space, runs the grouped GEMMs, forms the weighted sum of each copy's entries in fp32 and returns ONE
+bf16 row per copy; the source adds the partial rows of a token (+ shared expert). Bytes on the wire drop by
+the ratio entries / copies (2 x for 8 experts over 4 ranks). The split sizes are needed on the host, so
+the population exchange ends in a device-to-host copy per call.
 
 The bookkeeping (`ExchangePlan`) is integer tensor arithmetic that runs on any device; the compute is
 behind an `ops` object so that the same schedule runs over NCCL with the CUDA kernels (`CudaOps`) and,
@@ -95,13 +100,85 @@ def _all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, world: int, g
     return recv_b.view(send.dtype).reshape(-1, send.shape[1])
 
 
-def ep_moe_forward(x: torch.Tensor, ops, world: int, group=None, micro_batches: int = 1) -> torch.Tensor:
+def _all_to_all_counts(n_send: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    n_recv = torch.empty_like(n_send)
+    if world > 1:
+        dist.all_to_all_single(n_recv, n_send, group=group)
+    else:
+        n_recv.copy_(n_send)
+    return n_recv
+
+
+def _ep_dedup(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
+    """One copy of a token per destination rank; one partial result row per copy on the way back."""
+    dev, T, H = x.device, x.shape[0], x.shape[1]
+    nb = H // 128
+    idx, w = ops.route(x)                                           # [T, k]
+    k, e_local = idx.shape[1], ops.e_local
+    begin = getattr(ops, "shared_expert_begin", None)
+    pending = begin(x) if begin else None
+    # ---- copies: (destination rank, token) pairs in that order
+    dest = torch.div(idx, e_local, rounding_mode="floor").long()   # [T, k]
+    has = torch.zeros(T, world, dtype=torch.bool, device=dev).scatter_(1, dest, True)
+    has_t = has.t().contiguous().reshape(-1)                        # rank major, token minor
+    pos = torch.cumsum(has_t.to(torch.int64), 0) - 1
+    copy_pos = torch.where(has_t, pos, torch.full_like(pos, -1)).reshape(world, T).t().contiguous()   # [T, N]
+    n_send = has.sum(0).to(torch.int64)                             # [N]
+    n_recv = _all_to_all_counts(n_send, world, group)
+    send_splits, recv_splits = n_send.tolist(), n_recv.tolist()     # host sync
+    n_copies = sum(send_splits)
+    # ---- side band of a copy: its scales, then k slots of (weight, expert local to the destination or -1)
+    entry_copy = torch.gather(copy_pos, 1, dest)                    # [T, k] copy that carries entry (t, slot)
+    slot = torch.arange(k, device=dev).expand(T, k)
+    meta_e = torch.full((n_copies, k), -1, dtype=torch.int32, device=dev)
+    meta_w = torch.zeros(n_copies, k, dtype=torch.float32, device=dev)
+    meta_e[entry_copy, slot] = (idx.long() - dest * e_local).to(torch.int32)
+    meta_w[entry_copy, slot] = w.float()
+    copy_pos32 = copy_pos.to(torch.int32)
+    rows, scales = ops.quant_copies(x, copy_pos32, n_copies)
+    side = torch.cat([scales, meta_w, meta_e.view(torch.float32)], dim=1).contiguous()
+    recv_rows = _all_to_all_rows(rows, send_splits, recv_splits, world, group)
+    recv_side = _all_to_all_rows(side, send_splits, recv_splits, world, group)
+    R = recv_rows.shape[0]
+    r_scales = recv_side[:, :nb].contiguous()
+    r_w = recv_side[:, nb:nb + k].contiguous()
+    r_e = recv_side[:, nb + k:].contiguous().view(torch.int32)
+    # ---- entries of the received copies, sorted by local expert (stable: arrival order, then slot),
+    #      every expert's rows starting at a multiple of 128
+    key = r_e.reshape(-1).long()
+    key = torch.where(key >= 0, key, torch.full_like(key, e_local))
+    order = torch.argsort(key, stable=True)
+    local_counts = torch.bincount(key, minlength=e_local + 1)[:e_local]
+    padded = (local_counts + 127) // 128 * 128
+    n_entries, cap = int(local_counts.sum()), max(int(padded.sum()), 128)       # host sync
+    live = order[:n_entries]
+    live_e = key[live]
+    dst = _excl_cumsum(padded)[live_e] + torch.arange(n_entries, device=dev) - _excl_cumsum(local_counts)[live_e]
+    entry_row = torch.full((R * k,), -1, dtype=torch.int32, device=dev)
+    entry_row[live] = dst.to(torch.int32)
+    src_copy = torch.full((cap,), -1, dtype=torch.int32, device=dev)
+    src_copy[dst] = torch.div(live, k, rounding_mode="floor").to(torch.int32)
+    y = ops.expert_ffn_entries(recv_rows, r_scales, src_copy, local_counts.to(torch.int32), cap)   # [cap, H] bf16
+    partial = ops.combine(y, entry_row, r_w, None)                  # [R, H]: sum_j w_j y_j of each copy, fp32 -> bf16
+    back = _all_to_all_rows(partial, recv_splits, send_splits, world, group)
+    shared = ops.shared_expert_end(pending) if begin else ops.shared_expert(x)
+    return ops.combine(back, copy_pos32.reshape(-1), has.to(torch.float32), shared)
+
+
+def ep_moe_forward(x: torch.Tensor, ops, world: int, group=None, micro_batches: int = 1, dedup=None) -> torch.Tensor:
     """One layer call on this rank; `ops` supplies the compute (see CudaOps for the contract).
+
+    dedup (default: on when world > 1) sends a token once per destination rank, see the module text;
+    micro-batching applies to the per-entry form only.
 
     With micro_batches = 2 the local tokens are processed as two halves on two CUDA streams, issued in
     an interleaved order: the dispatch of the second half travels while the experts work on the first,
     and the first half's results travel back while the experts work on the second. The result does not
     depend on the split (every token is computed independently of its neighbours)."""
+    if dedup is None:
+        dedup = world > 1 and micro_batches <= 1
+    if dedup:
+        return _ep_dedup(x, ops, world, group)
     if micro_batches <= 1 or x.shape[0] < 2 * micro_batches:
         return _ep_pipeline([x], ops, world, group)[0]
     bounds = [x.shape[0] * i // micro_batches for i in range(micro_batches + 1)]
@@ -249,6 +326,33 @@ class CudaOps:
         y_recv = torch.empty(n, self.H, dtype=torch.bfloat16, device=self.dev)
         self.capi.moe_gather_rows(y_recv, y, plan.dst_row)
         return y_recv
+
+    # -- merged form: one copy of a token per destination rank
+    def quant_copies(self, x, copy_pos, n_copies):
+        """copy_pos int32 [T, N]: row of token t's copy for rank d in the send buffer, or -1."""
+        rows = torch.empty(n_copies, self.H, dtype=torch.uint8, device=self.dev)
+        scales = torch.empty(n_copies, self.H // 128, device=self.dev)
+        self.capi.moe_quant_rows(rows, scales, x, copy_pos.reshape(-1), copy_pos.shape[1])
+        return rows, scales
+
+    def expert_ffn_entries(self, recv_rows, recv_scales, src_copy, local_counts, cap):
+        """src_copy int32 [cap]: received copy behind every row of the padded row space (-1 = padding).
+        Returns y bf16 [cap, H] in that row space."""
+        i32 = dict(dtype=torch.int32, device=self.dev)
+        a_q = torch.empty(cap, self.H, dtype=torch.uint8, device=self.dev)
+        # the row gather moves 16-byte pieces: e4m3 rows are handed over as bf16 rows of half the length
+        if recv_rows.shape[0]:
+            self.capi.moe_gather_rows(a_q.view(torch.bfloat16), recv_rows.view(torch.bfloat16), src_copy)
+            a_s = recv_scales[src_copy.clamp(min=0).long()].t().contiguous()
+        else:                                     # nothing arrived: one tile of padding
+            a_q.zero_()
+            a_s = torch.ones(self.H // 128, cap, device=self.dev)
+        max_tiles = cap // 128
+        offsets, pad_offsets = torch.empty(self.e_local + 1, **i32), torch.empty(self.e_local + 1, **i32)
+        tile_expert, num_tiles = torch.empty(max_tiles, **i32), torch.empty(1, **i32)
+        self.capi.moe_tiles_from_counts(local_counts.contiguous(), offsets, pad_offsets, tile_expert, num_tiles)
+        return self._ffn(a_q, a_s, self.w13_q, self.w13_s, self.w2_q, self.w2_s, tile_expert, num_tiles, max_tiles,
+                         self.status[0:2])
 
     def shared_expert(self, x):
         if self.shared is None:

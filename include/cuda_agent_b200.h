@@ -174,7 +174,8 @@ int moe_tiles_from_counts_launcher(const int* counts, int E, int* offsets, int* 
 
 /* out[t,:] (bf16) = sum over slot = 0..k-1, in that order, of                   */
 /* weights[t,slot] * y[dst_row[t*k+slot], :] (+ extra[t,:] when non-NULL), fp32   */
-/* accumulation. y, extra, out are bf16 with row length H (H % 8 == 0).           */
+/* accumulation. y, extra, out are bf16 with row length H (H % 8 == 0). A slot    */
+/* whose dst_row is negative contributes nothing.                                  */
 int moe_combine_launcher(cab_bf16* out, const cab_bf16* y, const int* dst_row, const float* weights,
                          const cab_bf16* extra, int T, int H, int k, int config,
                          cab_stream_t stream);

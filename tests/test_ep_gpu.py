@@ -49,6 +49,11 @@ def test_world1_matches_oracle_and_fused_op(cuda_device, cfg, T):
                             sd["w2_s"], *sh, model.k, 0 if model.routing == "softmax" else 1, model.n_group,
                             model.topk_group, 1.0, True, 0)
     assert torch.equal(out, fused)                         # same kernels, same row order per expert
+    merged = ep_moe_forward(x.to(cuda_device), ops, 1, dedup=True)      # one copy per (token, rank), here one rank
+    torch.cuda.synchronize()
+    assert ops.status.cpu().tolist()[:2] == [0, 0]
+    rel_m = float((merged.float().cpu() - ref.float()).norm() / ref.float().norm())
+    assert rel_m <= 2e-2, rel_m
     out2 = ep_moe_forward(x.to(cuda_device), ops, 1, micro_batches=2)   # two halves on two streams
     torch.cuda.synchronize()
     assert torch.equal(out2, out)
