@@ -13,8 +13,8 @@ Data path of one layer call on rank r (T local tokens, k experts per token):
   return           all-to-all of the bf16 result rows, split sizes reversed               (NCCL)
   combine          weighted sum per token in slot order (+ shared expert)                 (kernel)
 
-That is `ep_moe_forward(..., dedup=False)`: an entry travels once per (token, slot). With more than one
-rank the default is the merged form (`_ep_dedup`): a token travels ONCE to every rank that holds at least
+That is `ep_moe_forward(..., dedup=False)`: an entry travels once per (token, slot). The default is the
+merged form (`_ep_dedup`; on one rank it still saves the copy of the results back into arrival order): a token travels ONCE to every rank that holds at least
 one of its experts (with group-limited routing at most `topk_group` ranks instead of k entries), together
 with a side band of k (local expert, weight) slots; the receiving rank expands the copies into its padded
 row space, runs the grouped GEMMs, forms the weighted sum of each copy's entries in fp32 and returns ONE
@@ -168,15 +168,15 @@ def _ep_dedup(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
 def ep_moe_forward(x: torch.Tensor, ops, world: int, group=None, micro_batches: int = 1, dedup=None) -> torch.Tensor:
     """One layer call on this rank; `ops` supplies the compute (see CudaOps for the contract).
 
-    dedup (default: on when world > 1) sends a token once per destination rank, see the module text;
-    micro-batching applies to the per-entry form only.
+    dedup (the default without micro-batching) sends a token once per destination rank, see the module
+    text; micro-batching applies to the per-entry form only.
 
     With micro_batches = 2 the local tokens are processed as two halves on two CUDA streams, issued in
     an interleaved order: the dispatch of the second half travels while the experts work on the first,
     and the first half's results travel back while the experts work on the second. The result does not
     depend on the split (every token is computed independently of its neighbours)."""
     if dedup is None:
-        dedup = world > 1 and micro_batches <= 1
+        dedup = micro_batches <= 1
     if dedup:
         return _ep_dedup(x, ops, world, group)
     if micro_batches <= 1 or x.shape[0] < 2 * micro_batches:

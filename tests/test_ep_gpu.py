@@ -36,7 +36,7 @@ def test_world1_matches_oracle_and_fused_op(cuda_device, cfg, T):
     model = m.Model(*args)
     ops = make_ops(model, cuda_device, 0, 1)
     x = torch.randn(T, model.H, generator=torch.Generator().manual_seed(T)).to(torch.bfloat16)
-    out = ep_moe_forward(x.to(cuda_device), ops, 1)
+    out = ep_moe_forward(x.to(cuda_device), ops, 1, dedup=False)      # one row per (token, expert)
     torch.cuda.synchronize()
     assert ops.status.cpu().tolist()[:2] == [0, 0]
     ref = model(x)
@@ -49,7 +49,7 @@ def test_world1_matches_oracle_and_fused_op(cuda_device, cfg, T):
                             sd["w2_s"], *sh, model.k, 0 if model.routing == "softmax" else 1, model.n_group,
                             model.topk_group, 1.0, True, 0)
     assert torch.equal(out, fused)                         # same kernels, same row order per expert
-    merged = ep_moe_forward(x.to(cuda_device), ops, 1, dedup=True)      # one copy per (token, rank), here one rank
+    merged = ep_moe_forward(x.to(cuda_device), ops, 1)                  # default: one copy per (token, rank)
     torch.cuda.synchronize()
     assert ops.status.cpu().tolist()[:2] == [0, 0]
     rel_m = float((merged.float().cpu() - ref.float()).norm() / ref.float().norm())
