@@ -2,8 +2,10 @@
 // token per sequence): out[b,h,:] = softmax_j(q[b,h,:] . kv[b, idx[b,j], :] * scale) . kv[b, idx[b,j], :512]
 // over the valid entries of idx (0 <= idx < seq_len[b]).
 //
-// One CTA handles 64 query heads of one sequence and one contiguous range ("split") of the
-// selected rows, 64 rows at a time:
+// Two kernels. Head groups of 128 run on pairs of CTAs that split the 576 columns between them
+// (mla_sparse_decode_pair_kernel, described further down); other head counts (multiples of 64), and
+// config 1, use the kernel described here: one CTA handles 64 query heads of one sequence and one
+// contiguous range ("split") of the selected rows, 64 rows at a time:
 //   producer warps (4)  gather the 64 selected cache rows (1152 B each) into shared memory with
 //                       16-byte cp.async copies, laid out as nine 64-row x 128-byte tiles in the
 //                       128-byte swizzle the tensor core reads; two stages
