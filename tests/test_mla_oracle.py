@@ -87,3 +87,23 @@ def test_several_query_tokens_per_sequence():
     out1 = m.Model(B, Hh, S, topk)(q, kv, seq_len[:, 0].contiguous(), idx)
     ref = mla_f64(q[:, 2:3], kv, seq_len[:, 0], idx[:, 2:3])
     assert np.abs(out1[:, 2:3].double().numpy() - ref).max() < 0.01 * np.abs(ref).max() + 4e-3
+
+
+def test_matches_committed_fixture():
+    """tests/golden/mla_small.npz (written by tests/golden/make_mla_moe_golden.py) pins the oracle over time."""
+    import importlib.util
+    from conftest import GOLDEN
+    spec = importlib.util.spec_from_file_location("make_mla_moe_golden", GOLDEN / "make_mla_moe_golden.py")
+    gen_mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen_mod)
+    fix = np.load(GOLDEN / "mla_small.npz")
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    for heads in (64, 128):
+        q, kv, seq_len, idx = gen_mod.mla_case(m, heads)
+        out = m.Model(2, heads, 300, 128)(q, kv, seq_len, idx)
+        got = out.reshape(-1)[::int(fix["stride"])].float().numpy()
+        want = torch.from_numpy(fix[f"out{heads}"].view(np.int16)).view(torch.bfloat16).float().numpy()
+        # the same arithmetic; a different thread count may move a sum by one bf16 step
+        assert np.mean(got == want) > 0.99
+        assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()
+

@@ -84,3 +84,26 @@ def test_config3_full_size(cuda_device):
     # run-to-run determinism of the whole layer
     out2 = run_layer(ext, model, sd, x.to(cuda_device))
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("cfg", [0, 1])
+def test_matches_committed_fixture(cuda_device, cfg):
+    """Against tests/golden/moe_config{cfg}.npz: routing indices bit for bit, output within rel-L2 2e-2."""
+    import numpy as np
+    from conftest import GOLDEN
+    import cuda_agent_b200
+    ext = cuda_agent_b200.load_extension()
+    fix = np.load(GOLDEN / f"moe_config{cfg}.npz")
+    m = load_oracle("moe", {"CAB_MOE_CONFIG": cfg})
+    m.reseed()
+    (x,) = m.get_inputs()
+    model = m.Model(*m.get_init_inputs())
+    sd = to_dev(model, cuda_device)
+    idx, w = ext.moe_route(x.to(cuda_device), sd["router_w"], sd["router_bias"], model.k,
+                           0 if model.routing == "softmax" else 1, model.n_group, model.topk_group, 1.0)
+    assert np.array_equal(idx.cpu().numpy(), fix["idx"])
+    np.testing.assert_allclose(w.cpu().numpy(), fix["w"], rtol=1e-4, atol=1e-6)
+    out = run_layer(ext, model, sd, x.to(cuda_device)).float().cpu()
+    want = torch.from_numpy(fix["out"].view(np.int16)).view(torch.bfloat16).float()
+    assert float((out - want).norm() / want.norm()) <= 2e-2
+

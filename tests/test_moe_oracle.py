@@ -180,3 +180,21 @@ def test_state_dict_names():
     assert {"router_w", "router_bias", "w13_q", "w13_s", "w2_q", "w2_s", "shared_w13_q", "shared_w13_s",
             "shared_w2_q", "shared_w2_s"} == names
     assert model.w13_q.dtype == torch.float8_e4m3fn and model.w13_s.shape == (16, 4, 2)
+
+
+@pytest.mark.parametrize("cfg", [0, 1])
+def test_matches_committed_fixture(cfg):
+    """tests/golden/moe_config{cfg}.npz (written by tests/golden/make_mla_moe_golden.py) pins the oracle over time."""
+    from conftest import GOLDEN
+    fix = np.load(GOLDEN / f"moe_config{cfg}.npz")
+    m = load_oracle("moe", {"CAB_MOE_CONFIG": cfg})
+    m.reseed()
+    (x,) = m.get_inputs()
+    model = m.Model(*m.get_init_inputs())
+    idx, w = model.route(model.logits(x))
+    assert np.array_equal(idx.numpy().astype(np.int32), fix["idx"])
+    np.testing.assert_allclose(w.numpy(), fix["w"], rtol=1e-5, atol=1e-7)
+    out = model(x).float().numpy()
+    want = torch.from_numpy(fix["out"].view(np.int16)).view(torch.bfloat16).float().numpy()
+    assert np.linalg.norm(out - want) <= 1e-3 * np.linalg.norm(want)
+
