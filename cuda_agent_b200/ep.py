@@ -123,10 +123,14 @@ def _ep_dedup(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
     has_t = has.t().contiguous().reshape(-1)                        # rank major, token minor
     pos = torch.cumsum(has_t.to(torch.int64), 0) - 1
     copy_pos = torch.where(has_t, pos, torch.full_like(pos, -1)).reshape(world, T).t().contiguous()   # [T, N]
-    n_send = has.sum(0).to(torch.int64)                             # [N]
+    # per destination: copies and entries; the entry totals let the receiver size its row space without a
+    # second device-to-host copy
+    n_send = torch.stack([has.sum(0).to(torch.int64),
+                          torch.bincount(dest.reshape(-1), minlength=world).to(torch.int64)], dim=1).contiguous()  # [N, 2]
     n_recv = _all_to_all_counts(n_send, world, group)
-    send_splits, recv_splits = n_send.tolist(), n_recv.tolist()     # host sync
-    n_copies = sum(send_splits)
+    send_host, recv_host = torch.stack([n_send, n_recv]).tolist()   # the one host sync of the call
+    send_splits, recv_splits = [c for c, _ in send_host], [c for c, _ in recv_host]
+    n_copies, n_entries = sum(send_splits), sum(e for _, e in recv_host)
     # ---- side band of a copy: its scales, then k slots of (weight, expert local to the destination or -1)
     entry_copy = torch.gather(copy_pos, 1, dest)                    # [T, k] copy that carries entry (t, slot)
     slot = torch.arange(k, device=dev).expand(T, k)
@@ -150,7 +154,9 @@ def _ep_dedup(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
     order = torch.argsort(key, stable=True)
     local_counts = torch.bincount(key, minlength=e_local + 1)[:e_local]
     padded = (local_counts + 127) // 128 * 128
-    n_entries, cap = int(local_counts.sum()), max(int(padded.sum()), 128)       # host sync
+    # rows of the padded space: at most 127 rows of padding per expert (the tile table on the device knows
+    # the exact extent; rows past it are never touched by a tile)
+    cap = max((n_entries + e_local * 127 + 127) // 128 * 128, 128)
     live = order[:n_entries]
     live_e = key[live]
     dst = _excl_cumsum(padded)[live_e] + torch.arange(n_entries, device=dev) - _excl_cumsum(local_counts)[live_e]
