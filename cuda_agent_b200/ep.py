@@ -100,6 +100,11 @@ def _all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, world: int, g
     return recv_b.view(send.dtype).reshape(-1, send.shape[1])
 
 
+def _count(values: torch.Tensor, bins: int) -> torch.Tensor:
+    """Occurrences of 0..bins-1 in `values` (int64), without the device-to-host copy torch.bincount makes."""
+    return torch.zeros(bins, dtype=torch.int64, device=values.device).scatter_add_(0, values, torch.ones_like(values))
+
+
 def _all_to_all_counts(n_send: torch.Tensor, world: int, group=None) -> torch.Tensor:
     n_recv = torch.empty_like(n_send)
     if world > 1:
@@ -126,7 +131,7 @@ def _ep_dedup(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
     # per destination: copies and entries; the entry totals let the receiver size its row space without a
     # second device-to-host copy
     n_send = torch.stack([has.sum(0).to(torch.int64),
-                          torch.bincount(dest.reshape(-1), minlength=world).to(torch.int64)], dim=1).contiguous()  # [N, 2]
+                          _count(dest.reshape(-1), world)], dim=1).contiguous()                      # [N, 2]
     n_recv = _all_to_all_counts(n_send, world, group)
     send_host, recv_host = torch.stack([n_send, n_recv]).tolist()   # the one host sync of the call
     send_splits, recv_splits = [c for c, _ in send_host], [c for c, _ in recv_host]
@@ -152,7 +157,7 @@ def _ep_dedup(x: torch.Tensor, ops, world: int, group=None) -> torch.Tensor:
     key = r_e.reshape(-1).long()
     key = torch.where(key >= 0, key, torch.full_like(key, e_local))
     order = torch.argsort(key, stable=True)
-    local_counts = torch.bincount(key, minlength=e_local + 1)[:e_local]
+    local_counts = _count(key, e_local + 1)[:e_local]
     padded = (local_counts + 127) // 128 * 128
     # rows of the padded space: at most 127 rows of padding per expert (the tile table on the device knows
     # the exact extent; rows past it are never touched by a tile)
