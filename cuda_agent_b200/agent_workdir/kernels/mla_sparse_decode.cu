@@ -83,6 +83,24 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// 16-column forms of the tensor-memory load and store (thread i: lane quadrant base + i, columns [col, col+16)).
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Operand descriptor for 128-byte-swizzled tiles; offsets in bytes.
@@ -454,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
 // Every wait is bounded; a CTA that gives up still reaches the closing cluster barrier, so its
 // partner's stores never hit shared memory of a CTA that has exited.
 constexpr int kPairHeads = 128;
-constexpr int kPairThreads = 18 * 32;              // 8 softmax, Q.K^T issuer, 4 producer, 4 exchange warps, P.V issuer
+constexpr int kPairThreads = 22 * 32;              // 8 softmax, Q.K^T issuer, 4 producer, 4 sending, P.V issuer, 4 receiving warps
 constexpr int kPairStages = 4;
 constexpr int kPairTiles = 2;                      // a stage lands in two parts: value tiles 0,1, then 2,3 and the rotary tile
 constexpr int kPairQRopeBytes = kPairHeads * 64;   // 128 heads x 32 rotary columns
@@ -465,8 +483,9 @@ constexpr int kPairPBytes = kPairHeads * 128;      // P: 128 heads x 64 tokens b
 constexpr uint32_t kPairColS = 0, kPairColQ = 128, kPairColO = 256;
 
 struct __align__(16) PairControl {
-  uint64_t kv_full[kPairStages][kPairTiles], kv_empty[kPairStages], s_full[2], s_ready[2], s_empty[2], p_full, p_empty[2],
-      x_full[2][2], x_free[2], o_done;   // p_empty, x_full: [even / odd blocks]; x_full, x_free: [.. column half]
+  uint64_t kv_full[kPairStages][kPairTiles], kv_empty[kPairStages], s_full[2], s_copied[2][2], s_ready[2], s_empty[2], p_full[2], p_empty[2],
+      x_full[2][2], x_free[2], o_done;   // p_full, p_empty, x_full: [even / odd blocks]; x_full, x_free: [.. column half]
+  uint64_t pub[4][2];                // [lane quadrant][even / odd blocks]: the row references after that block are published
   uint64_t duo[4];                   // the two softmax warps of a lane quadrant meet here (64 arrivals)
   uint32_t tmem_base;
   int abort_flag;
@@ -474,7 +493,7 @@ struct __align__(16) PairControl {
   float row_ref[kPairHeads];         // reference maximum of each head (log2 units) as the last block left it
   float row_sum[2][kPairHeads];      // [softmax group][head], used once at the end
 };
-constexpr int kPairSmemBytes = kPairQRopeBytes + kPairStages * kPairStageBytes + kPairXBytes + kPairPBytes +
+constexpr int kPairSmemBytes = kPairQRopeBytes + kPairStages * kPairStageBytes + kPairXBytes + 2 * kPairPBytes +
                                (int)sizeof(PairControl) + 1024;
 
 enum { kWaitXFull = 208, kWaitXFree = 209, kWaitDuo = 210 };
@@ -575,7 +594,7 @@ __device__ __forceinline__ void pair_produce(const MlaParams& p, PairControl& ct
   }
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(80)
 mla_sparse_decode_pair_kernel(const MlaParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -583,7 +602,7 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
   uint8_t* kv_tile = q_rope + kPairQRopeBytes;         // four stages
   uint8_t* x_tile = kv_tile + kPairStages * kPairStageBytes;   // float4 [16 column groups][128 heads]
   uint8_t* p_tile = x_tile + kPairXBytes;
-  PairControl& ctl = *reinterpret_cast<PairControl*>(p_tile + kPairPBytes);
+  PairControl& ctl = *reinterpret_cast<PairControl*>(p_tile + 2 * kPairPBytes);   // two P tiles (even / odd blocks)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = sm100::cluster_ctarank(), peer = rank ^ 1u;
   const int head0 = (blockIdx.x >> 1) * kPairHeads, split = blockIdx.y, b = blockIdx.z;
@@ -595,10 +614,14 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
     }
     for (int s = 0; s < 2; ++s) {
       sm100::mbar_init(&ctl.s_full[s], 1);
-      sm100::mbar_init(&ctl.s_ready[s], 4);           // the exchange warps have completed the scores
+      sm100::mbar_init(&ctl.s_copied[s][0], 4);       // the sending warps have read a half of the partial scores
+      sm100::mbar_init(&ctl.s_copied[s][1], 4);
+      sm100::mbar_init(&ctl.s_ready[s], 4);           // the receiving warps have completed the scores
       sm100::mbar_init(&ctl.s_empty[s], 4);           // the softmax warps of one group have read them
     }
-    sm100::mbar_init(&ctl.p_full, 4);
+    sm100::mbar_init(&ctl.p_full[0], 4);
+    sm100::mbar_init(&ctl.p_full[1], 4);
+    for (int s = 0; s < 8; ++s) sm100::mbar_init(&ctl.pub[s >> 1][s & 1], 1);
     sm100::mbar_init(&ctl.p_empty[0], 1);
     sm100::mbar_init(&ctl.p_empty[1], 1);
     for (int s = 0; s < 4; ++s) sm100::mbar_init(&ctl.x_full[s >> 1][s & 1], 1);   // one local arrival posts the bytes
@@ -659,73 +682,97 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
   const int len = __ldg(p.seq_len + b);
 
   if (warp >= 13 && warp <= 16) {
-    // ---------------------------------------------------------------- exchange warps (one per lane quadrant)
-    sm100::reg_dec<88>();
+    // ---------------------------------------------------------------- exchange, sending side (one warp per lane quadrant)
+    // Reads this CTA's partial scores from tensor memory 16 columns at a time and stores them into the
+    // other CTA's exchange buffer with asynchronous stores that count their bytes on that CTA's barrier.
+    // The buffer is used in two halves (score columns 0-31 and 32-63) with their own barriers, so that
+    // the other CTA may refill one half while the second is still being read. Sending and receiving are
+    // separate warps: the 32 KB of a block keep the path between the SMs busy for about 1.5 k clk, and
+    // the receiving side's waits and arithmetic run beside it instead of after it.
+    sm100::reg_dec<48>();
     const int quad = warp & 3;        // a warp reaches the tensor-memory lanes of quadrant warp % 4 only
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t peer_x = sm100::cluster_map(sm100::smem_u32(x_tile), peer);
-    // The exchange buffer is used in two halves (score columns 0-31 and 32-63) with their own barriers,
-    // so that the second half is on its way while the first is added, and the other CTA may refill the
-    // first half while the second is still being read.
     const uint32_t peer_bar0 = sm100::cluster_map(sm100::smem_u32(&ctl.x_full[0][0]), peer);   // [sb][half]: + 16 sb + 8 half
-    const uint32_t peer_free0 = sm100::cluster_map(sm100::smem_u32(&ctl.x_free[0]), peer);
-    const float4* x_own = reinterpret_cast<const float4*>(x_tile);
     bool ok = true;
-    for (int j = 0; j < nb; ++j) {
+    for (int j = 0; j < nb && ok; ++j) {
       const int sb = j & 1;
       if (!sm100::mbar_wait(&ctl.s_full[sb], (j >> 1) & 1, abort_flag, p.status, kWaitSFull)) ok = false;
       if (!__all_sync(0xffffffffu, ok)) break;
       sm100::tc_fence_after_sync();
-      uint32_t t0[32], t1[32];
-      sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok, t0);
-      sm100::tmem_ld_32x32(lane_base + kPairColS + sb * kTok + 32, t1);
-      sm100::tmem_ld_wait();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        // the other CTA's half buffer is free once its exchange warps have read block j-1 out of it
+        // the other CTA's half buffer is free once its receiving warps have read block j-1 out of it
         if (j >= 1 && !sm100::mbar_wait_cluster(&ctl.x_free[half], (j - 1) & 1, abort_flag, p.status, kWaitXFree))
           ok = false;
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-        // asynchronous stores that count their bytes on the other CTA's barrier when they land
         const uint32_t bar = peer_bar0 + 16 * sb + 8 * half;
-        const uint32_t (&t)[32] = half ? t1 : t0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          sm100::st_async_v4(peer_x + (uint32_t)(((half * 8 + i) * kPairHeads + row) * 16), bar, t[4 * i], t[4 * i + 1],
-                             t[4 * i + 2], t[4 * i + 3]);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t t[16];
+          tmem_ld_32x16(lane_base + kPairColS + sb * kTok + half * 32 + c * 16, t);
+          sm100::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            sm100::st_async_v4(peer_x + (uint32_t)(((half * 8 + c * 4 + i) * kPairHeads + row) * 16), bar, t[4 * i],
+                               t[4 * i + 1], t[4 * i + 2], t[4 * i + 3]);
+        }
+        // this half of the partial scores is in flight: the receiving warp may write the sums over it
+        sm100::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive(&ctl.s_copied[sb][half]);
       }
-      if (!ok) break;
-      // what the other CTA stored here: add it, hand each half back at once, and write the complete
-      // scores over the partial ones in tensor memory for the softmax warps
+    }
+  } else if (warp >= 18) {
+    // ---------------------------------------------------------------- exchange, receiving side (one warp per lane quadrant)
+    // Adds what the other CTA stored here to this CTA's partial scores, 16 columns at a time, writes the
+    // complete scores over the partial ones in tensor memory for the softmax warps and hands each half
+    // of the buffer back as soon as it has been read.
+    sm100::reg_dec<56>();
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t peer_free0 = sm100::cluster_map(sm100::smem_u32(&ctl.x_free[0]), peer);
+    const float4* x_own = reinterpret_cast<const float4*>(x_tile);
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      const int sb = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!sm100::mbar_wait(&ctl.s_full[sb], ph, abort_flag, p.status, kWaitSFull)) ok = false;
+      if (!__all_sync(0xffffffffu, ok)) break;
+      sm100::tc_fence_after_sync();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        if (!sm100::mbar_wait(&ctl.x_full[sb][half], (j >> 1) & 1, abort_flag, p.status, kWaitXFull)) ok = false;
+        if (!sm100::mbar_wait(&ctl.x_full[sb][half], ph, abort_flag, p.status, kWaitXFull) ||
+            !sm100::mbar_wait(&ctl.s_copied[sb][half], ph, abort_flag, p.status, kWaitSFull))
+          ok = false;
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        sm100::tc_fence_after_sync();
         if (quad == 0 && lane == 0 && j + 2 < nb)
           sm100::mbar_arrive_expect_tx(&ctl.x_full[sb][half], kPairXBytes / 2);   // block j+2
-        uint32_t (&t)[32] = half ? t1 : t0;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t t[16];
+          tmem_ld_32x16(lane_base + kPairColS + sb * kTok + half * 32 + c * 16, t);
           float4 xa[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) xa[i] = x_own[(half * 8 + h * 4 + i) * kPairHeads + row];
+          for (int i = 0; i < 4; ++i) xa[i] = x_own[(half * 8 + c * 4 + i) * kPairHeads + row];
+          sm100::tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint32_t* dst = &t[(h * 4 + i) * 4];
-            dst[0] = __float_as_uint(__uint_as_float(dst[0]) + xa[i].x);
-            dst[1] = __float_as_uint(__uint_as_float(dst[1]) + xa[i].y);
-            dst[2] = __float_as_uint(__uint_as_float(dst[2]) + xa[i].z);
-            dst[3] = __float_as_uint(__uint_as_float(dst[3]) + xa[i].w);
+            t[4 * i] = __float_as_uint(__uint_as_float(t[4 * i]) + xa[i].x);
+            t[4 * i + 1] = __float_as_uint(__uint_as_float(t[4 * i + 1]) + xa[i].y);
+            t[4 * i + 2] = __float_as_uint(__uint_as_float(t[4 * i + 2]) + xa[i].z);
+            t[4 * i + 3] = __float_as_uint(__uint_as_float(t[4 * i + 3]) + xa[i].w);
           }
+          tmem_st_32x16(lane_base + kPairColS + sb * kTok + half * 32 + c * 16, t);
         }
         // every value read from this half has been used: it may be overwritten
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive_cluster_relaxed(peer_free0 + 8 * half);
       }
       if (!ok) break;
-      tmem_st_32x32(lane_base + kPairColS + sb * kTok, t0);
-      tmem_st_32x32(lane_base + kPairColS + sb * kTok + 32, t1);
       tmem_st_wait();
       sm100::tc_fence_before_sync();
       __syncwarp();
@@ -741,7 +788,7 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
     // ---------------------------------------------------------------- Q.K^T issuer
     // Two issuing threads (this one and the P.V issuer in warp 17) instead of one that polls: each
     // simply waits for what it needs next, and the tensor core takes their instructions as they come.
-    sm100::reg_dec<56>();
+    sm100::reg_dec<40>();
     if (lane == 0) {
       constexpr uint32_t idesc_qk = sm100::umma_idesc(1 /* bf16 */, kPairHeads, kTok);
       const uint64_t a_rope = umma_desc_sw64(sm100::smem_u32(q_rope));
@@ -773,14 +820,14 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
     __syncwarp();
   } else if (warp == 17) {
     // ---------------------------------------------------------------- P.V issuer
-    sm100::reg_dec<56>();
+    sm100::reg_dec<40>();
     if (lane == 0) {
       constexpr uint32_t idesc_pv = sm100::umma_idesc(1, kPairHeads, 256) | (1u << 16);   // B is MN-major
-      const uint64_t a = umma_desc_sw128(sm100::smem_u32(p_tile), 16, 1024);
       bool ok = true;
       for (int j = 0; j < nb; ++j) {
         const int st = j % kPairStages;
-        if (!sm100::mbar_wait(&ctl.p_full, j & 1, abort_flag, p.status, kWaitPFull)) { ok = false; break; }
+        if (!sm100::mbar_wait(&ctl.p_full[j & 1], (j >> 1) & 1, abort_flag, p.status, kWaitPFull)) { ok = false; break; }
+        const uint64_t a = umma_desc_sw128(sm100::smem_u32(p_tile + (j & 1) * kPairPBytes), 16, 1024);
         sm100::tc_fence_after_sync();
         const uint64_t bd = umma_desc_sw128(sm100::smem_u32(kv_tile + st * kPairStageBytes), kChunkBytes, 1024);
 #pragma unroll
@@ -795,17 +842,17 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax + epilogue (warps 0..7)
-    // 18 warps leave 96 registers per thread at launch. Registers are handed over inside each SM
-    // sub-partition (warps w, w+4, w+8, ...: two softmax warps, a producer, an exchange warp, and an
-    // issuing warp in sub-partitions 0 and 1): 2 x 120 + 56 + 88 (+ 56) <= 4 (5) x 96.
+    // 22 warps launch with 80 registers per thread. Registers are handed over inside each SM
+    // sub-partition (warps w, w+4, w+8, ...: two softmax warps, a producer, a sending and a receiving
+    // warp, and an issuing warp in sub-partitions 0 and 1): 2 x 120 + 56 + 48 + 56 (+ 40) <= 5 (6) x 80.
     sm100::reg_inc<120>();
     // Two groups of four warps take the blocks in turn (group 0 the even ones, group 1 the odd ones), one
     // thread per head with all 64 scores of the block, so that the waits of one block hide behind the
-    // arithmetic of the other. What orders the blocks is the single P tile: P of block j is written after
-    // P.V of block j-1 has finished. At that point the thread reads the row's reference maximum as block
-    // j-1 left it, decides about raising it, and publishes it for block j+1. The exponentials are computed
-    // earlier against the reference the thread could see then, and once more in the rare case that it
-    // changed in between.
+    // arithmetic of the other. Each group has its own P tile. What orders the blocks is a small barrier per
+    // lane quadrant: a warp finishes block j only after the other group's warp of the same quadrant has
+    // published the rows' reference maxima after block j-1; then the thread reads its row's reference,
+    // decides about raising it, and publishes it for block j+1. The exponentials are computed earlier
+    // against the reference the thread could see then, and once more in the rare case that it changed.
     const int quad = warp & 3, grp = warp >> 2;
     const int row = quad * 32 + lane;                  // head inside the 128; tensor-memory lane
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -866,17 +913,24 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
       const float m_guess = next_ref(m_shared[row]);   // block j-1 may not have published yet
       exponentials(m_guess);
 
-      // P, O and the row's reference may be touched only after P.V of block j-1 has finished
-      if (j >= 1 && !sm100::mbar_wait(&ctl.p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitPEmpty))
+      // This block's P tile (one for the even, one for the odd blocks) is free once P.V of block j-2 has
+      // finished; the row references are final once block j-1 has published them.
+      if (j >= 2 && !sm100::mbar_wait(&ctl.p_empty[j & 1], ((j - 2) >> 1) & 1, abort_flag, p.status, kWaitPEmpty))
+        ok = false;
+      if (j >= 1 && !sm100::mbar_wait(&ctl.pub[quad][(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitDuo))
         ok = false;
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-      sm100::tc_fence_after_sync();
       const float m_prev = m_shared[row];
       const float m_new = next_ref(m_prev);
       if (m_new != m_guess) exponentials(m_new);
       // O holds sums relative to m_prev
       const float factor = (m_prev != -INFINITY && m_new != m_prev) ? exp2f(m_prev - m_new) : 1.f;
       if (__any_sync(0xffffffffu, factor != 1.f)) {
+        // rare: O is rescaled in place, which needs P.V of block j-1 to have finished
+        if (j >= 1 && !sm100::mbar_wait(&ctl.p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kWaitPEmpty))
+          ok = false;
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        sm100::tc_fence_after_sync();
 #pragma unroll 1
         for (int c = 0; c < 256; c += 32) {
           uint32_t o[32];
@@ -895,7 +949,7 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
       l_part += psum;
       m_shared[row] = m_new;
       {
-        uint8_t* prow = p_tile + row * 128;
+        uint8_t* prow = p_tile + (j & 1) * kPairPBytes + row * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c)
           *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
@@ -904,7 +958,10 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
       sm100::fence_proxy_async();
       sm100::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&ctl.p_full);
+      if (lane == 0) {
+        sm100::mbar_arrive(&ctl.pub[quad][j & 1]);      // the references of this warp's rows are final for block j
+        sm100::mbar_arrive(&ctl.p_full[j & 1]);
+      }
     }
 
     // ------------------------------------------------------------ epilogue
