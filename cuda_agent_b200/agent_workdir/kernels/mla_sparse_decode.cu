@@ -751,22 +751,30 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
         sm100::tc_fence_after_sync();
         if (quad == 0 && lane == 0 && j + 2 < nb)
           sm100::mbar_arrive_expect_tx(&ctl.x_full[sb][half], kPairXBytes / 2);   // block j+2
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t t[16];
-          tmem_ld_32x16(lane_base + kPairColS + sb * kTok + half * 32 + c * 16, t);
-          float4 xa[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) xa[i] = x_own[(half * 8 + c * 4 + i) * kPairHeads + row];
+        {
+          // both 16-column loads of the half are issued before the wait, so that their round trips overlap
+          uint32_t t[32];
+          uint32_t (&ta)[16] = *reinterpret_cast<uint32_t(*)[16]>(&t[0]);
+          uint32_t (&tb)[16] = *reinterpret_cast<uint32_t(*)[16]>(&t[16]);
+          tmem_ld_32x16(lane_base + kPairColS + sb * kTok + half * 32, ta);
+          tmem_ld_32x16(lane_base + kPairColS + sb * kTok + half * 32 + 16, tb);
           sm100::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            t[4 * i] = __float_as_uint(__uint_as_float(t[4 * i]) + xa[i].x);
-            t[4 * i + 1] = __float_as_uint(__uint_as_float(t[4 * i + 1]) + xa[i].y);
-            t[4 * i + 2] = __float_as_uint(__uint_as_float(t[4 * i + 2]) + xa[i].z);
-            t[4 * i + 3] = __float_as_uint(__uint_as_float(t[4 * i + 3]) + xa[i].w);
+          for (int c = 0; c < 2; ++c) {
+            float4 xa[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xa[i] = x_own[(half * 8 + c * 4 + i) * kPairHeads + row];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t* d4 = &t[c * 16 + 4 * i];
+              d4[0] = __float_as_uint(__uint_as_float(d4[0]) + xa[i].x);
+              d4[1] = __float_as_uint(__uint_as_float(d4[1]) + xa[i].y);
+              d4[2] = __float_as_uint(__uint_as_float(d4[2]) + xa[i].z);
+              d4[3] = __float_as_uint(__uint_as_float(d4[3]) + xa[i].w);
+            }
           }
-          tmem_st_32x16(lane_base + kPairColS + sb * kTok + half * 32 + c * 16, t);
+          tmem_st_32x16(lane_base + kPairColS + sb * kTok + half * 32, ta);
+          tmem_st_32x16(lane_base + kPairColS + sb * kTok + half * 32 + 16, tb);
         }
         // every value read from this half has been used: it may be overwritten
         __syncwarp();
