@@ -141,3 +141,15 @@ def test_ep_schedule_over_gloo_world2(tmp_path, cfg):
         res = torch.load(tmp_path / f"rank{rank}.pt")
         assert res["rel"] < 2e-3, res                      # same arithmetic, only bf16 rounding order differs
         assert res["rel_merged"] < 6e-3, res               # + one bf16 rounding of the partial sum per (token, rank)
+
+
+def test_ep_schedule_over_gloo_world4(tmp_path):
+    """Four ranks, 16 experts in 4 groups (one group per rank), top-4 over 2 groups: a token reaches at most two
+    ranks, so the merged form sends at most two copies where the per-entry form sends four rows."""
+    port = 29850 + (os.getpid() % 100)
+    mp.spawn(_worker, args=(4, port, 1, str(tmp_path)), nprocs=4, join=True)
+    for rank in range(4):
+        res = torch.load(tmp_path / f"rank{rank}.pt")
+        assert res["rel"] < 2e-3, res
+        assert res["rel_merged"] < 6e-3, res
+
