@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../../include/cuda_agent_b200.h"
 
 namespace cab {
@@ -19,6 +21,24 @@ __host__ __device__ inline bool aligned_to(const void* p, size_t bytes) {
 // Status a launcher returns after enqueueing: catches bad launch configurations
 // without synchronising the stream.
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? CAB_OK : CAB_ERR_LAUNCH; }
+
+// Opt-in to more than 48 KB of dynamic shared memory for `Kernel`. The attribute belongs to the
+// (function, device) pair, so it is set once per device with that device current; one process may
+// drive several GPUs and several host threads.
+constexpr int kMaxDevices = 64;
+template <auto Kernel>
+inline bool ensure_dynamic_smem(int bytes) {
+  static std::mutex mu;
+  static bool done[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    done[dev] = true;
+  }
+  return true;
+}
 
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_sparse_decode_kernel(const Ml
   const int per_split = (blocks_total + p.nsplit - 1) / p.nsplit;
   const int j0 = split * per_split;
   const int nb = max(0, min(blocks_total, j0 + per_split) - j0);
-  const int len = __ldg(p.seq_len + b);
+  const int len = min(__ldg(p.seq_len + b), p.S);   // a length past the cache's extent never reaches a row outside it
 
   if (warp >= 5) {
     // ---------------------------------------------------------------- producers
@@ -679,7 +679,7 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
   const int per_split = (blocks_total + p.nsplit - 1) / p.nsplit;
   const int j0 = split * per_split;
   const int nb = max(0, min(blocks_total, j0 + per_split) - j0);
-  const int len = __ldg(p.seq_len + b);
+  const int len = min(__ldg(p.seq_len + b), p.S);   // a length past the cache's extent never reaches a row outside it
 
   if (warp >= 13 && warp <= 16) {
     // ---------------------------------------------------------------- exchange, sending side (one warp per lane quadrant)
@@ -1087,7 +1087,7 @@ mla_gather_rows_kernel(uint4* __restrict__ rows, const uint4* __restrict__ kv, c
   const long long rowid = id / 72;
   const int b = (int)(rowid / topk);
   const int t = __ldg(idx + rowid);
-  const bool ok = t >= 0 && t < __ldg(seq_len + b);
+  const bool ok = t >= 0 && t < min(__ldg(seq_len + b), S);
   rows[id] = ok ? __ldg(kv + ((size_t)b * S + t) * 72 + piece) : make_uint4(0, 0, 0, 0);
 }
 
@@ -1113,13 +1113,6 @@ extern "C" int mla_sparse_decode_multi_launcher(cab_bf16* out, const cab_bf16* q
   if (!cab::aligned_to(out, 16) || !cab::aligned_to(q, 16) || !cab::aligned_to(kv, 16) ||
       (scratch && !cab::aligned_to(scratch, 16)))
     return CAB_ERR_MISALIGNED;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(mla_sparse_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-        cudaSuccess)
-      return CAB_ERR_LAUNCH;
-    configured = true;
-  }
   MlaParams p;
   p.q = reinterpret_cast<const __nv_bfloat16*>(q);
   p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);
@@ -1133,15 +1126,10 @@ extern "C" int mla_sparse_decode_multi_launcher(cab_bf16* out, const cab_bf16* q
   if (status && cudaMemsetAsync(status, 0, sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
   // config 1 forces the single-CTA kernel (64 heads per CTA); otherwise 128-head groups run on CTA pairs
   if (config != 1 && Hh % kPairHeads == 0) {
-    static bool pair_configured = false;
-    if (!pair_configured) {
-      if (cudaFuncSetAttribute(mla_sparse_decode_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               kPairSmemBytes) != cudaSuccess)
-        return CAB_ERR_LAUNCH;
-      pair_configured = true;
-    }
+    if (!cab::ensure_dynamic_smem<&mla_sparse_decode_pair_kernel>(kPairSmemBytes)) return CAB_ERR_LAUNCH;
     mla_sparse_decode_pair_kernel<<<dim3(2 * (Hh / kPairHeads), nsplit, B), kPairThreads, kPairSmemBytes, stream>>>(p);
   } else {
+    if (!cab::ensure_dynamic_smem<&mla_sparse_decode_kernel>(kSmemBytes)) return CAB_ERR_LAUNCH;
     mla_sparse_decode_kernel<<<dim3(Hh / kHeads, nsplit, B), kThreads, kSmemBytes, stream>>>(p);
   }
   int rc = cab::launch_status();
@@ -1219,6 +1207,8 @@ extern "C" int mla_sparse_decode_noalloc_launcher(cab_bf16* out, const cab_bf16*
                                                   int config, cudaStream_t stream) {
   if (B == 0) return CAB_OK;
   if (B < 0 || Hh <= 0 || nsplit <= 0) return CAB_ERR_BAD_ARGUMENT;
+  // every factor is bounded before the product is formed, so it cannot wrap
+  if (B > 65535 || nsplit > 65535 || Hh > 65535) return CAB_ERR_TOO_LARGE;
   // (B * nsplit * Hh) slots of 512 + 2 floats must fit the fixed array
   const unsigned long long need = (unsigned long long)B * (unsigned long long)nsplit * (unsigned long long)Hh *
                                   (kDv + 2) * sizeof(float);

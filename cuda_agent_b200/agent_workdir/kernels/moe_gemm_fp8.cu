@@ -340,13 +340,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 template <int MODE>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tout, const GemmParams& p, int grid,
            cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(moe_gemm_fp8_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem_bytes<MODE>()) != cudaSuccess)
-      return CAB_ERR_LAUNCH;
-    configured = true;
-  }
+  if (!cab::ensure_dynamic_smem<&moe_gemm_fp8_kernel<MODE>>(smem_bytes<MODE>())) return CAB_ERR_LAUNCH;
   moe_gemm_fp8_kernel<MODE><<<grid, kThreads, smem_bytes<MODE>(), stream>>>(ta, tb, tout, p);
   return cab::launch_status();
 }

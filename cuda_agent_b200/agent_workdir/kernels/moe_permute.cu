@@ -26,14 +26,16 @@ constexpr int kTileM = 128;
 // wc[w][e] = number of entries of expert e among warp w's 32 consecutive entries.
 __device__ __forceinline__ void chunk_warp_counts(int (*wc)[kMaxE], const int* __restrict__ idx,
                                                   int n, int E, int& my_e, int& rank_in_warp,
-                                                  bool& out_of_range) {
+                                                  bool& out_of_range, bool empty_ok = false) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) wc[i / E][i % E] = 0;
   __syncthreads();
   const int i = blockIdx.x * kChunk + threadIdx.x;
   my_e = i < n ? __ldg(idx + i) : -1;
-  out_of_range = i < n && (my_e < 0 || my_e >= E);
-  if (out_of_range) my_e = -1;   // flagged by the caller, otherwise ignored
+  // Ids outside [0, E) are skipped and flagged; with empty_ok, -1 is the expected marker of an empty
+  // slot (an unused slot of a fixed-capacity receive buffer) and is skipped without a flag.
+  out_of_range = i < n && (my_e < (empty_ok ? -1 : 0) || my_e >= E);
+  if (my_e < 0 || my_e >= E) my_e = -1;
   // lanes past the end all carry -1 and only match each other
   const unsigned peers = __match_any_sync(0xffffffffu, my_e);
   rank_in_warp = __popc(peers & ((1u << lane) - 1u));
@@ -88,12 +90,12 @@ moe_count_scan_kernel(const int* __restrict__ idx, int n, int E, int nchunks,
                       unsigned* __restrict__ done_counter,
                       int* __restrict__ counts, int* __restrict__ offsets,
                       int* __restrict__ pad_offsets, int* __restrict__ tile_expert,
-                      int* __restrict__ num_tiles, int max_tiles, int* __restrict__ status) {
+                      int* __restrict__ num_tiles, int max_tiles, int* __restrict__ status, bool empty_ok) {
   __shared__ int wc[32][kMaxE];
   __shared__ bool is_last;
   int my_e, rank;
   bool bad;
-  chunk_warp_counts(wc, idx, n, E, my_e, rank, bad);
+  chunk_warp_counts(wc, idx, n, E, my_e, rank, bad, empty_ok);
   if (bad && status) atomicExch(status, 1);   // expert id out of range: flagged, entry ignored
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int c = 0;
@@ -107,16 +109,25 @@ moe_count_scan_kernel(const int* __restrict__ idx, int n, int E, int nchunks,
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // exclusive scan over chunks, one thread per expert
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int run = 0;
-    for (int c = 0; c < nchunks; ++c) {
-      const int v = __ldcg(chunk_cnt + (size_t)c * E + e);
-      chunk_cnt[(size_t)c * E + e] = run;
-      run += v;
+  // exclusive scan over chunks: a warp per expert, 32 chunks per shuffle scan
+  {
+    const int lane = threadIdx.x & 31;
+    for (int e = threadIdx.x >> 5; e < E; e += kChunk / 32) {
+      int run = 0;
+      for (int c0 = 0; c0 < nchunks; c0 += 32) {
+        const int c = c0 + lane;
+        const int v = c < nchunks ? __ldcg(chunk_cnt + (size_t)c * E + e) : 0;
+        int inc = v;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int a = __shfl_up_sync(0xffffffffu, inc, off);
+          if (lane >= off) inc += a;
+        }
+        if (c < nchunks) chunk_cnt[(size_t)c * E + e] = run + inc - v;
+        run += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) { counts[e] = run; wc[0][e] = run; }
     }
-    counts[e] = run;
-    wc[0][e] = run;
   }
   __syncthreads();
   build_tile_table(wc[0], E, offsets, pad_offsets, tile_expert, num_tiles, max_tiles, status, &wc[1][0]);
@@ -140,13 +151,20 @@ moe_rank_kernel(const int* __restrict__ idx, int n, int E, const int* __restrict
   }
   __syncthreads();
   const int i = blockIdx.x * kChunk + threadIdx.x;
-  if (i < n && my_e >= 0) {
+  if (i >= n) return;
+  if (my_e >= 0) {
     const int within = __ldg(chunk_base + (size_t)blockIdx.x * E + my_e) + wc[threadIdx.x >> 5][my_e] + rank;
     const int pos = __ldg(offsets + my_e) + within;
     inv_perm[i] = pos;
     perm[pos] = i;
     dst_row[i] = __ldg(pad_offsets + my_e) + within;
+  } else {
+    // a skipped entry has no row: the quantise-dispatch and combine kernels pass over negative rows
+    inv_perm[i] = -1;
+    dst_row[i] = -1;
   }
+  // sorted positions past the last valid entry name no entry
+  if (i >= __ldg(offsets + E)) perm[i] = -1;
 }
 
 // ------------------------------------------------------------------ quantise + dispatch
@@ -290,7 +308,7 @@ moe_tiles_from_counts_kernel(const int* __restrict__ counts, int E, int* __restr
 
 extern "C" size_t moe_permute_scratch_bytes(int T, int k, int E) {
   const long long n = (long long)T * k;
-  const long long nchunks = (n + kChunk - 1) / kChunk;
+  const long long nchunks = n <= 0 ? 1 : (n + kChunk - 1) / kChunk;   // the launcher runs one chunk when empty
   return (size_t)(nchunks * E + 2) * sizeof(int);
 }
 
@@ -304,7 +322,6 @@ extern "C" int moe_permute_launcher(const int* topk_idx, int T, int k, int E, in
                                     int* offsets, int* pad_offsets, int* perm, int* inv_perm,
                                     int* dst_row, int* tile_expert, int* num_tiles, int max_tiles,
                                     void* scratch, int config, cudaStream_t stream) {
-  (void)config;
   if (!counts || !offsets || !pad_offsets || !tile_expert || !num_tiles || !scratch)
     return CAB_ERR_BAD_ARGUMENT;
   if (T < 0 || k <= 0 || E <= 0 || E > kMaxE || max_tiles <= 0) return CAB_ERR_BAD_ARGUMENT;
@@ -318,7 +335,7 @@ extern "C" int moe_permute_launcher(const int* topk_idx, int T, int k, int E, in
   if (cudaMemsetAsync(done, 0, 2 * sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
   moe_count_scan_kernel<<<nchunks, kChunk, 0, stream>>>(topk_idx, (int)n, E, nchunks, chunk_cnt, done,
                                                         counts, offsets, pad_offsets, tile_expert,
-                                                        num_tiles, max_tiles, status);
+                                                        num_tiles, max_tiles, status, (config & 1) != 0);
   if (n > 0)
     moe_rank_kernel<<<nchunks, kChunk, 0, stream>>>(topk_idx, (int)n, E, chunk_cnt, offsets,
                                                     pad_offsets, perm, inv_perm, dst_row);

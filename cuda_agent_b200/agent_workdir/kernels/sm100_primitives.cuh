@@ -62,21 +62,26 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` lives in shared memory; `status` (global, may be
 // null) receives `where` the first time any wait in the grid gives up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int where) {
+// `limit` is the number of clock cycles after which the wait gives up.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, int where, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, where);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int where) {
+  return mbar_wait_limited(bar, parity, abort_flag, status, where, kWaitLimitCycles);
 }
 
 // Same, polling gently: for a thread that runs far ahead of its consumer (a TMA producer) and

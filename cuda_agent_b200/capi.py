@@ -17,6 +17,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libcuda_agent_b200.so"
 SIGNATURES = {
     "cab_status_string": (c_char_p, [c_int]),
     "cab_version": (c_int, []),
+    "cab_wait_selftest": (c_int, [c_void_p, ctypes.c_longlong, c_int, c_void_p]),
     "axpby_launcher": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p]),
     "gdn_decode_launcher": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p]),
     "moe_router_logits_launcher": (c_int, [c_void_p] * 3 + [c_int] * 4 + [c_void_p]),
@@ -85,6 +86,12 @@ def _p(t) -> int:
     return t.data_ptr()
 
 
+def wait_selftest(status, limit_cycles: int, withhold: bool) -> None:
+    """Runs the bounded-wait self-test kernel; `status` (int32 [1], CUDA) receives 0 or the give-up code 901."""
+    _check("cab_wait_selftest",
+           lib().cab_wait_selftest(_p(status), int(limit_cycles), int(bool(withhold)), _stream()))
+
+
 def axpby(out, a, b, alpha: float, config: int = 0) -> None:
     _check("axpby_launcher",
            lib().axpby_launcher(_p(out), _p(a), _p(b), alpha, a.numel(), config, _stream()))
@@ -126,8 +133,9 @@ def moe_route_sigmoid_group_topk(topk_idx, topk_w, logits, bias, n_group, topk_g
                                                        config, _stream()))
 
 
-def moe_permute(topk_idx, E: int):
-    """Allocates and returns the permutation tables for topk_idx [T, k] (int32, CUDA)."""
+def moe_permute(topk_idx, E: int, config: int = 0):
+    """Allocates and returns the permutation tables for topk_idx [T, k] (int32, CUDA).
+    config bit 0: an id of -1 marks an empty slot and is skipped without raising the flag."""
     import torch
     T, k = topk_idx.shape
     dev = topk_idx.device
@@ -143,7 +151,7 @@ def moe_permute(topk_idx, E: int):
            lib().moe_permute_launcher(_p(topk_idx), T, k, E, _p(out["counts"]), _p(out["offsets"]),
                                       _p(out["pad_offsets"]), _p(out["perm"]), _p(out["inv_perm"]),
                                       _p(out["dst_row"]), _p(out["tile_expert"]), _p(out["num_tiles"]),
-                                      max_tiles, _p(scratch), 0, _stream()))
+                                      max_tiles, _p(scratch), config, _stream()))
     out["scratch"] = scratch
     return out
 

@@ -53,6 +53,14 @@ const char* cab_status_string(int status);
 /* Library version as major*10000 + minor*100 + patch. */
 int cab_version(void);
 
+/* Self-test of the bounded waits inside the tensor-core kernels (no counterpart */
+/* in the reference, whose one kernel never waits). One small CTA waits on a      */
+/* barrier for at most limit_cycles clock cycles (1 .. 1e9); with withhold != 0    */
+/* the barrier's last arrival never comes, the wait gives up, *status (device int) */
+/* becomes 901 and the kernel returns through its normal teardown; with withhold   */
+/* == 0 the wait completes and *status stays 0. The device stays usable either way. */
+int cab_wait_selftest(int* status, long long limit_cycles, int withhold, cab_stream_t stream);
+
 /* ------------------------------------------------------------------------- */
 /* axpby: the workspace's smoke-test op.                                      */
 /* Replaces agent_workdir/kernels/axpby.cu:12-42 (same argument order).       */
@@ -136,8 +144,12 @@ int moe_permute_max_tiles(int T, int k, int E);
 /*   num_tiles[1]                 tiles in use                                    */
 /* scratch: moe_permute_scratch_bytes() bytes of device memory, contents         */
 /* irrelevant on entry. Positions come from scans, never from atomics, so the     */
-/* result equals a CPU stable sort on every run. Out-of-range expert ids are      */
-/* skipped and flagged in the last int of scratch (1), as is tile overflow (2).   */
+/* result equals a CPU stable sort on every run. An entry whose expert id lies     */
+/* outside [0, E) is skipped: inv_perm and dst_row hold -1 for it, the tail of     */
+/* perm past the valid entries holds -1, and the last int of scratch is set to 1   */
+/* (tile overflow sets it to 2). With config bit 0 set, an id of exactly -1 is the */
+/* expected marker of an empty slot and is skipped without the flag. T*k == 0 is    */
+/* allowed (every table is written for zero entries).                              */
 int moe_permute_launcher(const int* topk_idx, int T, int k, int E, int* counts, int* offsets,
                          int* pad_offsets, int* perm, int* inv_perm, int* dst_row, int* tile_expert,
                          int* num_tiles, int max_tiles, void* scratch, int config,
@@ -208,7 +220,9 @@ int moe_grouped_gemm_fp8_launcher(int mode, void* out, float* out_scales_t, cons
 /* the kernel slot of agent_workdir/kernels/ (ABI of axpby.cu:12-20).            */
 /*   q        bf16 [B, 1, Hh, 576]   (512 latent + 64 rope dims), Hh % 64 == 0   */
 /*   kv       bf16 [B, S, 576]       latent KV cache                             */
-/*   seq_len  int32 [B]              valid rows per sequence                     */
+/*   seq_len  int32 [B]              valid rows per sequence; a value above S   */
+/*                                   is read as S, so no row outside the cache   */
+/*                                   is ever touched                             */
 /*   idx      int32 [B, 1, topk]     selected rows, shared by all heads; an      */
 /*                                   entry counts iff 0 <= idx < seq_len[b]      */
 /*   out      bf16 [B, 1, Hh, 512] = softmax(q . kv[idx]^T * softmax_scale)      */

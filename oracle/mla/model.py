@@ -24,6 +24,7 @@ shared cache with its own selection and valid length.
 entries give zero rows); it is compared bit for bit.
 
 ``CAB_MLA_CONFIG``: 0 = CPU-sized (B=3, 16 heads, S=300, topk=64);
+1 = B=3, 64 heads, S=600, topk=320 (the smallest head count the CUDA operator takes);
 2 = B=64, 128 heads, S=32768, topk=2048, lengths uniform in [8192, 32768].
 """
 import os
@@ -35,6 +36,7 @@ D_QK, D_V = 576, 512
 SCALE = 192 ** -0.5
 CONFIGS = {
     0: dict(B=3, Hh=16, S=300, topk=64, min_len=40),
+    1: dict(B=3, Hh=64, S=600, topk=320, min_len=200),
     2: dict(B=64, Hh=128, S=32768, topk=2048, min_len=8192),
 }
 CONFIG = int(os.environ.get("CAB_MLA_CONFIG", "0"))

@@ -159,31 +159,37 @@ class Model(nn.Module):
     """forward(x bf16 [T, H]) -> out bf16 [T, H]."""
 
     def __init__(self, T, H, I, E, k, routing="softmax", n_group=1, topk_group=1, shared=False,
-                 routed_scaling_factor=1.0, seed=4321):
+                 routed_scaling_factor=1.0, seed=4321, device=None):
+        """device: where the synthetic weights are drawn and kept (default CPU; the large configs are
+        drawn on a GPU, whose generator gives a different but equally seeded stream)."""
         super().__init__()
         assert H % BLK == 0 and I % BLK == 0 and E % n_group == 0
         self.T, self.H, self.I, self.E, self.k = T, H, I, E, k
         self.routing, self.n_group, self.topk_group = routing, n_group, topk_group
         self.routed_scaling_factor = routed_scaling_factor
-        gen = torch.Generator().manual_seed(seed)
-        self.router_w = nn.Parameter((torch.randn(E, H, generator=gen) * 0.02).to(torch.bfloat16),
-                                     requires_grad=False)
-        self.register_buffer("router_bias", torch.randn(E, generator=gen) * 0.02)
-        w13_q = torch.empty(E, 2 * I, H, dtype=torch.float8_e4m3fn)
-        w13_s = torch.empty(E, 2 * I // BLK, H // BLK)
-        w2_q = torch.empty(E, H, I, dtype=torch.float8_e4m3fn)
-        w2_s = torch.empty(E, H // BLK, I // BLK)
+        dev = torch.device("cpu" if device is None else device)
+        gen = torch.Generator(device=dev).manual_seed(seed)
+
+        def randn(*shape):
+            return torch.randn(*shape, generator=gen, device=dev)
+
+        self.router_w = nn.Parameter((randn(E, H) * 0.02).to(torch.bfloat16), requires_grad=False)
+        self.register_buffer("router_bias", randn(E) * 0.02)
+        w13_q = torch.empty(E, 2 * I, H, dtype=torch.float8_e4m3fn, device=dev)
+        w13_s = torch.empty(E, 2 * I // BLK, H // BLK, device=dev)
+        w2_q = torch.empty(E, H, I, dtype=torch.float8_e4m3fn, device=dev)
+        w2_s = torch.empty(E, H // BLK, I // BLK, device=dev)
         for e in range(E):  # one expert at a time keeps the fp32 staging small
-            w13_q[e], w13_s[e] = quant_128x128(torch.randn(2 * I, H, generator=gen) * 0.02)
-            w2_q[e], w2_s[e] = quant_128x128(torch.randn(H, I, generator=gen) * 0.02)
+            w13_q[e], w13_s[e] = quant_128x128(randn(2 * I, H) * 0.02)
+            w2_q[e], w2_s[e] = quant_128x128(randn(H, I) * 0.02)
         for name, t in (("w13_q", w13_q), ("w13_s", w13_s), ("w2_q", w2_q), ("w2_s", w2_s)):
             self.register_buffer(name, t)
         self.has_shared = bool(shared)
         if shared:
-            q, s = quant_128x128(torch.randn(2 * I, H, generator=gen) * 0.02)
+            q, s = quant_128x128(randn(2 * I, H) * 0.02)
             self.register_buffer("shared_w13_q", q)
             self.register_buffer("shared_w13_s", s)
-            q, s = quant_128x128(torch.randn(H, I, generator=gen) * 0.02)
+            q, s = quant_128x128(randn(H, I) * 0.02)
             self.register_buffer("shared_w2_q", q)
             self.register_buffer("shared_w2_s", s)
 

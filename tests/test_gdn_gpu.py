@@ -139,6 +139,29 @@ def test_full_size_properties(cuda_device):
     assert int((S == S0).sum()) < S.numel() // 10000
 
 
+def test_full_size_after_1_and_64_steps(cuda_device):
+    """Config 1 (B=256, 16/32 heads): 64 chained decode steps with fresh inputs per step; sampled batch
+    rows are compared with the oracle stepping just those rows, after step 1 and after step 64."""
+    from cuda_agent_b200 import capi
+    m = load_oracle("gdn", {"CAB_GDN_CONFIG": 1})
+    B, Hq, Hv = m.get_init_inputs()
+    dev = cuda_device
+    gd = torch.Generator(device=dev).manual_seed(4321)
+    S = torch.randn(B, Hv, 128, 128, device=dev, generator=gd) * 0.02
+    pick = torch.tensor([0, 101, 255])
+    S_ref = S[pick].cpu()
+    model = m.Model(len(pick), Hq, Hv)
+    out = torch.empty(B, Hv, 128, device=dev)
+    gen = torch.Generator().manual_seed(4322)
+    for step in range(64):
+        inputs = m.make_step_inputs(B, Hq, Hv, gen)
+        capi.gdn_decode(S, out, *[t.to(dev) for t in inputs])
+        o_ref, S_ref = model(S_ref, *[t[pick] for t in inputs])
+        if step in (0, 63):
+            assert_rel(out[pick], o_ref, what=f"o after step {step + 1}")
+            assert_rel(S[pick], S_ref, what=f"state after step {step + 1}")
+
+
 def test_extension_and_verification_loop(cuda_device, built_libs, capsys):
     """The reference-style gate: oracle model.py vs tasks/gdn/model_new.py, 5 trials."""
     import sys

@@ -24,7 +24,10 @@ def check_status(status):
     assert int(status) == 0, f"kernel wait gave up at code {int(status)}"
 
 
-@pytest.mark.parametrize("rows,N,K", [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (384, 2048, 1024)])
+# the last two: the down projection of the expert-parallel layer (N 7168, K 2048) and 56 K blocks (K 7168), where
+# the per-lane weight-scale registers use their second half
+@pytest.mark.parametrize("rows,N,K", [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (384, 2048, 1024),
+                                      (256, 7168, 2048), (128, 512, 7168)])
 def test_dense_down_projection(cuda_device, rows, N, K):
     from cuda_agent_b200 import capi
     m = load_oracle("moe", {"CAB_MOE_CONFIG": 0})
@@ -43,7 +46,8 @@ def test_dense_down_projection(cuda_device, rows, N, K):
     assert rel < 3e-3, rel
 
 
-@pytest.mark.parametrize("rows,I,K", [(128, 128, 128), (256, 256, 512), (128, 1024, 2048)])
+# the last one: gate/up of the expert-parallel layer (I 2048, K 7168 = 56 K blocks)
+@pytest.mark.parametrize("rows,I,K", [(128, 128, 128), (256, 256, 512), (128, 1024, 2048), (256, 2048, 7168)])
 def test_dense_gate_up_swiglu_requant(cuda_device, rows, I, K):
     from cuda_agent_b200 import capi
     m = load_oracle("moe", {"CAB_MOE_CONFIG": 0})
@@ -97,3 +101,22 @@ def test_grouped_pipeline_matches_oracle(cuda_device, T, H, I, E, k):
     assert status.cpu().tolist() == [0, 0]
     rel = float((out.float().cpu() - ref.float()).norm() / ref.float().norm())
     assert rel < 2e-2, rel
+
+
+def test_bounded_wait_gives_up_and_the_kernel_returns(cuda_device):
+    """The wait protocol of the tensor-core kernels: an arrival that never comes makes the wait run out after
+    its cycle limit; the kernel records the give-up code, goes through its teardown (tensor memory freed) and
+    returns, and the device keeps working. With the arrival present the same kernel reports 0."""
+    from cuda_agent_b200 import capi
+    status = torch.full((1,), -1, dtype=torch.int32, device=cuda_device)
+    capi.wait_selftest(status, 200_000, withhold=False)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    capi.wait_selftest(status, 200_000, withhold=True)       # about 0.1 ms at 1.9 GHz
+    torch.cuda.synchronize()
+    assert int(status) == 901
+    # tensor memory was released and the context is healthy: a real GEMM runs right after
+    capi.wait_selftest(status, 200_000, withhold=False)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    test_dense_down_projection(cuda_device, 128, 256, 128)

@@ -103,6 +103,96 @@ def test_permutation_flags_bad_expert_ids(cuda_device):
     assert res["counts"].cpu().tolist() == [1, 1, 1, 0]
 
 
+def test_permutation_skips_invalid_entries(cuda_device):
+    """Entries without a valid expert (-1 from a router that ran out of finite candidates, ids >= E) get
+    no row: inv_perm = dst_row = -1, the tail of perm is -1, the rest is the stable sort of the valid ones."""
+    from cuda_agent_b200 import capi
+    m = load_oracle("moe", {"CAB_MOE_CONFIG": 0})
+    gen = torch.Generator().manual_seed(3)
+    T, k, E = 700, 4, 16
+    idx = torch.randint(0, E, (T, k), generator=gen, dtype=torch.int32)
+    idx[5] = -1                                  # a token with no expert at all
+    idx[::7, 2] = -1
+    idx[300, 0] = E + 3
+    valid = (idx >= 0) & (idx < E)
+    flat_valid = valid.reshape(-1)
+    # oracle on the valid entries only, mapped back to flat positions
+    keys = idx.reshape(-1)[flat_valid]
+    order = torch.argsort(keys.long(), stable=True)
+    where = torch.nonzero(flat_valid).reshape(-1)
+    perm_ref = torch.full((T * k,), -1, dtype=torch.int32); perm_ref[: len(order)] = where[order].to(torch.int32)
+    inv_ref = torch.full((T * k,), -1, dtype=torch.int32); inv_ref[where[order]] = torch.arange(len(order), dtype=torch.int32)
+    counts = torch.bincount(keys.long(), minlength=E)
+    for config, flag in ((0, 1), (1, 1)):        # the id E + 3 is flagged either way
+        res = capi.moe_permute(idx.to(cuda_device), E, config)
+        torch.cuda.synchronize()
+        assert torch.equal(res["counts"].cpu().long(), counts)
+        assert torch.equal(res["perm"].cpu(), perm_ref) and torch.equal(res["inv_perm"].cpu(), inv_ref)
+        dst = res["dst_row"].cpu()
+        assert bool((dst[~flat_valid] == -1).all()) and bool((dst[flat_valid] >= 0).all())
+        assert int(res["scratch"].view(torch.int32)[-1]) == flag
+    idx[300, 0] = 1                              # only -1 markers left: flagged without config bit 0, silent with it
+    assert int(capi.moe_permute(idx.to(cuda_device), E, 0)["scratch"].view(torch.int32)[-1]) == 1
+    assert int(capi.moe_permute(idx.to(cuda_device), E, 1)["scratch"].view(torch.int32)[-1]) == 0
+
+
+def test_nan_token_is_dropped_without_stray_writes(cuda_device):
+    """A NaN activation row leaves the router without candidates (-1 in every slot). Its entries must get
+    no row: nothing is written outside the padded row space and the token's combined output is zero."""
+    from cuda_agent_b200 import capi
+    gen = torch.Generator().manual_seed(8)
+    T, H, E, k = 40, 256, 8, 2
+    x = torch.randn(T, H, generator=gen).to(torch.bfloat16)
+    x[7] = float("nan")
+    wr = (torch.randn(E, H, generator=gen) * 0.02).to(torch.bfloat16)
+    dev = cuda_device
+    logits = torch.empty(T, E, device=dev)
+    capi.moe_router_logits(logits, x.to(dev), wr.to(dev))
+    idx, w = i32(T, k, dev=dev), torch.empty(T, k, device=dev)
+    capi.moe_route_softmax_topk(idx, w, logits)
+    assert idx[7].cpu().tolist() == [-1] * k
+    res = capi.moe_permute(idx, E)
+    assert int(res["scratch"].view(torch.int32)[-1]) == 1
+    assert res["dst_row"].view(T, k)[7].cpu().tolist() == [-1] * k
+    cap, guard = res["max_tiles"] * 128, 8
+    big_q = torch.full((cap + 2 * guard, H), 0xAA, dtype=torch.uint8, device=dev)
+    big_s = torch.full((H // 128, cap + 2 * guard), -1.0, device=dev)
+    # the row space is a view with poisoned guard rows on both sides
+    capi.moe_quant_dispatch(big_q[guard:], big_s, x.to(dev), res["dst_row"], k)
+    torch.cuda.synchronize()
+    assert bool((big_q[:guard] == 0xAA).all()) and bool((big_q[guard + cap:] == 0xAA).all())
+    written = (big_q[guard:guard + cap] != 0xAA).any(dim=1).sum()
+    assert int(written) <= (T - 1) * k
+    y = torch.randn(cap, H, generator=gen).to(torch.bfloat16).to(dev)
+    out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device=dev)
+    capi.moe_combine(out, y, res["dst_row"], torch.nan_to_num(w), None)
+    assert bool((out[7] == 0).all()) and bool(torch.isfinite(out.float()).all())
+
+
+def test_permutation_of_an_empty_batch(cuda_device):
+    """T = 0 with 256 experts: the tables are written for zero entries and nothing past the scratch
+    size the library asks for is touched."""
+    from cuda_agent_b200 import capi
+    E, k = 256, 8
+    lib = capi.lib()
+    need = lib.moe_permute_scratch_bytes(0, k, E)
+    assert need >= (E + 2) * 4
+    guard = 4096
+    buf = torch.full((need + guard,), 0x5C, dtype=torch.uint8, device=cuda_device)
+    i32k = dict(dtype=torch.int32, device=cuda_device)
+    counts, offsets, pad = torch.full((E,), -7, **i32k), torch.full((E + 1,), -7, **i32k), torch.full((E + 1,), -7, **i32k)
+    max_tiles = lib.moe_permute_max_tiles(0, k, E)
+    tile_expert, num_tiles = torch.full((max_tiles,), -7, **i32k), torch.full((1,), -7, **i32k)
+    rc = lib.moe_permute_launcher(None, 0, k, E, counts.data_ptr(), offsets.data_ptr(), pad.data_ptr(), None, None,
+                                  None, tile_expert.data_ptr(), num_tiles.data_ptr(), max_tiles, buf.data_ptr(), 0,
+                                  torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert bool((buf[need:] == 0x5C).all())
+    assert int(counts.abs().sum()) == 0 and int(offsets.abs().sum()) == 0 and int(pad.abs().sum()) == 0
+    assert int(num_tiles) == 0 and bool((tile_expert == -1).all())
+
+
 @pytest.mark.parametrize("T,H,k", [(96, 256, 2), (40, 2048, 6), (9, 7168, 8), (5, 128, 1), (33, 384, 3)])
 def test_quant_dispatch_exact(cuda_device, T, H, k):
     from cuda_agent_b200 import capi
