@@ -1,36 +1,45 @@
 #!/usr/bin/env python3
-"""Headline benchmark: Gated DeltaNet decode at serving scale, in GB/s.
+"""Benchmark of the three decode/inference hot paths; the headline is Gated DeltaNet decode in GB/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload all|gdn|moe|mla|moe_ep]
 
-Workload ("gdn_decode_serving"): B=256 sequences per GPU, 16 q/k heads shared by
-groups of 2 across 32 value heads, dk=dv=128, fp32 state of 512 MiB per GPU. One
-step is one decode step (one kernel launch over the whole batch) with that
-step's own q/k/v/g/beta, taken in turn from 64 pre-generated seeded steps.
-Algorithmic bytes per step per GPU: state read + write 2*536870912, q and k
+One JSON line on rank 0. Headline workload ("gdn_decode_serving"): B=256 sequences per GPU, 16 q/k heads
+shared by groups of 2 across 32 value heads, dk=dv=128, fp32 state of 512 MiB per GPU. One step is one decode
+step (one kernel launch over the whole batch) with that step's own q/k/v/g/beta, taken in turn from 64
+pre-generated seeded steps. Algorithmic bytes per step per GPU: state read + write 2*536870912, q and k
 2*1048576, v 2097152, g and beta 2*32768, o 4194304 = 1082195968.
 
-Printed keys (one JSON line, rank 0):
-  value      GB/s over all GPUs with every input already in HBM (CUDA events, max over ranks)
-  e2e        same metric through cuda_extension.gdn_decode_forward with the step's
-             q/k/v/g/beta coming from pinned host memory and o going back to it,
-             copies inside the timed region (the 512 MiB state lives on the GPU
-             between steps, as it does in a serving process)
-  roofline   the decode kernel against measured HBM copy bandwidth
-  cpu_baseline  the eager oracle on this box's host cores (a reported baseline)
-  clocks     SM clock and throttle reasons sampled during the timed regions
+Keys of the line:
+  value        GB/s over all GPUs with every input already in HBM (CUDA events, max over ranks)
+  e2e          same metric through cuda_extension.gdn_decode_forward with the step's inputs coming from
+               pinned host memory and o going back to it, copies inside the timed region (the 512 MiB
+               state lives on the GPU between steps, as it does in a serving process)
+  roofline     the decode kernel against measured HBM copy bandwidth
+  cpu_baseline the eager oracle on this box's host cores (a reported baseline; N=1 only)
+  clocks       SM clock and throttle reasons sampled during the timed regions
+  secondary    with --workload all (the default), one record per other path, each with its own value,
+               ms_per_step, e2e, roofline and (N=1) cpu_baseline:
+                 moe     FP8 MoE layer, 4096 tokens, 64 experts, top-6 (one GPU by definition: N=1 only)
+                 mla     top-2048 sparse MLA decode, 64 sequences x 128 heads per GPU (batch-sharded)
+                 moe_ep  expert-parallel FP8 MoE layer, 8192 tokens per GPU, 256 experts over the ranks,
+                         with `parity` = rel-L2 of 256 tokens of rank 0 against the eager oracle's functions
 
-With N > 1 the batch is sharded with no collective: every rank runs the same
-per-GPU workload on its own state (weak scaling); NCCL is used only for the
-barrier and the max over ranks.
+Every timed region lasts at least MIN_REGION_S seconds: when the requested --steps finish sooner, the
+region is repeated with more steps, and the number of steps actually timed is what the line reports
+("steps"; the request is kept in "steps_requested").
 
-``--impl reference`` times the eager CPU oracle (the reference's torch-eager path
-for this operator) on the host cores instead; rank 0 only.
+With N > 1 GDN and MLA are sharded by batch with no collective (every rank runs the same per-GPU workload:
+weak scaling); the expert-parallel layer exchanges rows between the ranks. NCCL carries the barrier and
+the max over ranks.
+
+``--impl reference`` times the eager CPU oracles (the reference's torch-eager path for these operators)
+on all host cores instead; rank 0 only. The rates it prints are those of one host and do not depend on N.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import sys
 import threading
@@ -40,16 +49,17 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-D = 128
-B, HQ, HV = 256, 16, 32
-N_DISTINCT_STEPS = 64
-BYTES_PER_STEP = 2 * B * HV * D * D * 4 + 2 * B * HQ * D * 2 + B * HV * D * 2 + 2 * B * HV * 4 + B * HV * D * 4
-H2D_BYTES = 2 * B * HQ * D * 2 + B * HV * D * 2 + 2 * B * HV * 4
-D2H_BYTES = B * HV * D * 4
+MIN_REGION_S = 0.5
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one gdn_decode_kernel launch at this
-# workload, from the ncu capture summarised in profiles/gdn_decode_kernel_config1.md.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1025223168
+FALLBACK_BF16_TFLOPS = 1590.0
+NOMINAL_FP8_TFLOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures of each kernel at
+# these workloads (the summaries under profiles/ give the commands).
+NCU_TRAFFIC = {
+    "gdn_decode_v8_kernel<8>": 1025223168,
+    "moe_gemm_fp8_kernel<0> + <1>": 355400000 + 246100000,
+    "mla_sparse_decode_pair_kernel": 166300000,
+}
 
 
 def parse_args():
@@ -60,16 +70,16 @@ def parse_args():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--config", type=int, default=0, help="launcher variant passed to the op")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-dedup", action="store_true",
-                    help="moe_ep: send one row per (token, expert) instead of one per (token, destination rank)")
     ap.add_argument("--graph", action="store_true",
                     help="gdn: also time the loop recorded as CUDA graphs (extra key \"cuda_graph\")")
-    ap.add_argument("--workload", choices=["gdn", "moe", "mla", "moe_ep"], default="gdn",
-                    help="gdn = the headline line; moe = FP8 MoE layer (4096 tokens, 64 experts, top-6); "
-                         "mla = top-2048 sparse MLA decode (64 sequences, 128 heads)")
-    ap.add_argument("--micro-batches", type=int, default=1,
-                    help="moe_ep: token micro-batches pipelined over streams (with --config C < 148 GEMM CTAs)")
-    ap.add_argument("--nsplit", type=int, default=1, help="mla: splits of the selected rows per CTA group")
+    ap.add_argument("--workload", choices=["all", "gdn", "moe", "mla", "moe_ep"], default="all",
+                    help="all = headline GDN line with the other paths under \"secondary\"; a single name = "
+                         "that path alone as the line")
+    ap.add_argument("--ep-mode", choices=["peer", "nccl"], default="peer",
+                    help="moe_ep: rows pushed into the peers' receive buffers by the kernels themselves (peer) "
+                         "or exchanged with NCCL all-to-all calls (nccl)")
+    ap.add_argument("--nsplit", type=int, default=0, help="mla: splits of the selected rows (0 = the op's choice)")
+    ap.add_argument("--min-region-s", type=float, default=MIN_REGION_S)
     return ap.parse_args()
 
 
@@ -142,474 +152,393 @@ class ClockSampler:
                 "samples": len(inside), "scope": scope}
 
 
-# --------------------------------------------------------------------------- reference arm
-def load_oracle():
-    import importlib.util
-    os.environ["CAB_GDN_CONFIG"] = "1"
-    spec = importlib.util.spec_from_file_location("gdn_oracle_model", ROOT / "oracle" / "gdn" / "model.py")
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    return mod
+def load_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        p = json.loads(f.read_text())
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "source": "fallback"}
 
 
-def time_oracle_cpu(n_steps: int, n_warmup: int, budget_s: float):
-    """Eager oracle on the host cores. Returns (GB/s, seconds per step, sample text, threads)."""
-    import torch
-    m = load_oracle()
-    threads = torch.get_num_threads()
-    gen = torch.Generator().manual_seed(1235)
-    # calibrate on 8 batch rows, then pick the batch sample that fits the budget
-    model = m.Model(8, HQ, HV)
-    S = m.make_state(8, HV, gen)
-    step = m.make_step_inputs(8, HQ, HV, gen)
-    with torch.no_grad():
-        model(S, *step)
-        t0 = time.perf_counter()
-        model(S, *step)
-        per_row = (time.perf_counter() - t0) / 8
-    total_steps = max(1, n_steps + n_warmup)
-    b_sample = int(min(B, max(8, budget_s / (per_row * total_steps))))
-    b_sample -= b_sample % 8
-    model = m.Model(b_sample, HQ, HV)
-    S = m.make_state(b_sample, HV, gen)
-    steps = [m.make_step_inputs(b_sample, HQ, HV, gen) for _ in range(min(4, total_steps))]
-    with torch.no_grad():
-        for i in range(n_warmup):
-            _, S = model(S, *steps[i % len(steps)])
-        t0 = time.perf_counter()
-        for i in range(n_steps):
-            _, S = model(S, *steps[i % len(steps)])
-        dt = (time.perf_counter() - t0) / max(1, n_steps)
-    gbs = BYTES_PER_STEP * (b_sample / B) / dt / 1e9
-    sample = f"{n_steps} steps of {b_sample} of the {B} batch rows (all 32 value heads), torch eager fp32"
-    return gbs, dt, sample, threads
+# --------------------------------------------------------------------------- run context
+class Ctx:
+    """Ranks, barrier, and timed regions of at least `min_s` seconds whose length every rank agrees on."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.args = torch, dist, args
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device (the operators have no CPU path)")
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.sampler = ClockSampler(self.local_rank)
+        self.sampler.start()
+        self.windows = []
+        self.peaks = load_peaks()
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, value: float) -> float:
+        t = self.torch.tensor([value], device=self.dev, dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t)
+
+    def timed(self, step, steps, warmup, wall=False, run_n=None):
+        """(ms per step as the max over ranks, steps timed). `step(i)` enqueues step i; with run_n given, the
+        region is run_n(n) (a pipelined loop that ends synchronised) and is timed by the host clock, otherwise
+        by CUDA events on the current stream. The region is repeated with more steps until it lasts min_s."""
+        torch = self.torch
+        stream = torch.cuda.current_stream()
+
+        def region(n):
+            self.barrier()
+            w0 = time.monotonic()
+            if run_n is not None:
+                t0 = time.perf_counter()
+                run_n(n)
+                torch.cuda.synchronize()
+                ms = (time.perf_counter() - t0) * 1e3
+            else:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for i in range(n):
+                    step(i)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1)
+            self.barrier()
+            self.windows.append((w0, time.monotonic()))
+            return self.max_over_ranks(ms)
+
+        if run_n is not None:
+            run_n(max(3, warmup))
+        else:
+            for i in range(max(3, warmup)):
+                step(i)
+        n = max(1, steps)
+        ms = region(n)
+        min_ms = self.args.min_region_s * 1e3
+        if ms < min_ms:
+            n = int(math.ceil(n * min_ms * 1.1 / max(ms, 1e-3)))
+            ms = region(n)
+        return ms / n, n
+
+    def finish(self):
+        self.sampler.stop()
+        clocks = self.sampler.summary(self.windows)
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+        return clocks
 
 
-def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    gbs, dt, sample, threads = time_oracle_cpu(args.steps, args.warmup, budget_s=150.0)
-    line = {
-        "impl": "reference", "metric": "gdn_decode_gbps", "value": round(gbs, 3), "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line), flush=True)
-
-
-def workload_config(n_gpus):
-    return {"workload": "gdn_decode_serving", "B_per_gpu": B, "Hq": HQ, "Hv": HV, "dk": D, "dv": D,
-            "state_bytes_per_gpu": B * HV * D * D * 4, "distinct_steps": N_DISTINCT_STEPS,
-            "bytes_per_step_per_gpu": BYTES_PER_STEP, "parallelism": f"batch-sharded x{n_gpus}, no collective",
-            "l2": "state (512 MiB) exceeds L2 (126 MB); no flush needed"}
-
-
-# --------------------------------------------------------------------------- B200 arm
-def make_device_steps(torch, dev, seed):
-    """64 decode steps' inputs with the workload's distributions, generated on the device."""
-    gen = torch.Generator(device=dev).manual_seed(seed)
-    n = N_DISTINCT_STEPS
-    q = torch.randn(n, B, HQ, D, device=dev, generator=gen)
-    q = (q / q.norm(dim=-1, keepdim=True)).to(torch.bfloat16)
-    k = torch.randn(n, B, HQ, D, device=dev, generator=gen)
-    k = (k / k.norm(dim=-1, keepdim=True)).to(torch.bfloat16)
-    v = torch.randn(n, B, HV, D, device=dev, generator=gen).to(torch.bfloat16)
-    g = -torch.nn.functional.softplus(torch.randn(n, B, HV, device=dev, generator=gen))
-    beta = torch.sigmoid(torch.randn(n, B, HV, device=dev, generator=gen))
-    state = torch.randn(B, HV, D, D, device=dev, generator=gen) * 0.02
-    return state, q, k, v, g, beta
-
-
-def run_b200(args):
-    import torch
-    import torch.distributed as dist
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device (the operators have no CPU path)")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    from cuda_agent_b200 import capi, load_extension
-    ext = load_extension()
-    capi.lib()
-
-    state, q, k, v, g, beta = make_device_steps(torch, dev, 1235 + rank)
-    out = torch.empty(B, HV, D, device=dev)
-    stream = torch.cuda.current_stream()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    windows = []
-
-    # ---- device-resident timing through the C ABI
-    def step(i):
-        j = i % N_DISTINCT_STEPS
-        capi.gdn_decode(state, out, q[j], k[j], v[j], g[j], beta[j], args.config)
-
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    w0 = time.monotonic()
-    ev0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    ev1.record(stream)
-    barrier()
-    windows.append((w0, time.monotonic()))
-    ms_total = ev0.elapsed_time(ev1)
-    assert bool(torch.isfinite(out).all()), "non-finite decode output"
-
-    # ---- the same loop recorded as CUDA graphs of N_DISTINCT_STEPS launches each (reported beside the headline)
-    graph_ms = None
+# --------------------------------------------------------------------------- the four paths (B200 arm)
+def gdn_record(ctx: Ctx, cpu_baseline: bool):
+    import bench_workloads as bw
+    args, torch = ctx.args, ctx.torch
+    wl = bw.GdnWorkload(ctx.dev, 1235 + ctx.rank)
+    ms, n = ctx.timed(lambda i: wl.step(i, args.config), args.steps, args.warmup)
+    assert bool(torch.isfinite(wl.out).all()), "non-finite decode output"
+    graph = None
     if args.graph:
         from cuda_agent_b200.graphs import GdnDecodeGraph
-        gdn_graph = GdnDecodeGraph(state, out, q, k, v, g, beta, args.config)
-        replays = max(1, args.steps // N_DISTINCT_STEPS)
-        gdn_graph.replay()
-        barrier()
-        w0 = time.monotonic()
-        ev0.record(stream)
-        for _ in range(replays):
-            gdn_graph.replay()
-        ev1.record(stream)
-        barrier()
-        windows.append((w0, time.monotonic()))
-        graph_ms = ev0.elapsed_time(ev1) / (replays * N_DISTINCT_STEPS)
-
-    # ---- end to end through the extension op, host buffers in, host buffer out
-    pin = lambda t: t.cpu().pin_memory()
-    hq, hk, hv_, hg, hb = pin(q), pin(k), pin(v), pin(g), pin(beta)
-    ho = torch.empty(2, B, HV, D).pin_memory()
-    dq = [torch.empty_like(q[0]) for _ in range(2)]
-    dk = [torch.empty_like(k[0]) for _ in range(2)]
-    dv = [torch.empty_like(v[0]) for _ in range(2)]
-    dg = [torch.empty_like(g[0]) for _ in range(2)]
-    db = [torch.empty_like(beta[0]) for _ in range(2)]
-    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-    in_ready = [torch.cuda.Event() for _ in range(2)]
-    in_free = [torch.cuda.Event() for _ in range(2)]
-    out_done = [torch.cuda.Event() for _ in range(2)]
-
-    def e2e_loop(n):
-        """Double-buffered: inputs of step i+1 upload while step i computes; o downloads behind it."""
-        def upload(i):
-            s, j = i % 2, i % N_DISTINCT_STEPS
-            with torch.cuda.stream(copy_in):
-                copy_in.wait_event(in_free[s])
-                dq[s].copy_(hq[j], non_blocking=True); dk[s].copy_(hk[j], non_blocking=True)
-                dv[s].copy_(hv_[j], non_blocking=True); dg[s].copy_(hg[j], non_blocking=True)
-                db[s].copy_(hb[j], non_blocking=True)
-                in_ready[s].record(copy_in)
-        for e in in_free:
-            e.record(stream)
-        upload(0)
-        for i in range(n):
-            s = i % 2
-            if i + 1 < n:
-                upload(i + 1)
-            stream.wait_event(in_ready[s])
-            o, _ = ext.gdn_decode_forward(state, dq[s], dk[s], dv[s], dg[s], db[s], args.config)
-            in_free[s].record(stream)
-            done = torch.cuda.Event()
-            done.record(stream)
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(done)
-                ho[s].copy_(o, non_blocking=True)
-                o.record_stream(copy_out)
-                out_done[s].record(copy_out)
-        copy_out.synchronize()
-
-    for e in out_done:
-        e.record(copy_out)
-    e2e_loop(min(args.warmup, 16))
-    barrier()
-    w0 = time.monotonic()
-    t0 = time.perf_counter()
-    e2e_loop(args.steps)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    barrier()
-    windows.append((w0, time.monotonic()))
-    sampler.stop()
-
-    # ---- max over ranks
-    times = torch.tensor([ms_total, e2e_s * 1e3], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = float(times[0]), float(times[1])
-    ms_per_step = ms_total / args.steps
-    value = BYTES_PER_STEP * world / (ms_per_step * 1e-3) / 1e9
-    e2e_value = BYTES_PER_STEP * world / (e2e_ms / args.steps * 1e-3) / 1e9
-    per_gpu = value / world
-
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    if peaks_file.exists():
-        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    else:
-        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
-
-    if rank == 0:
-        line = {
-            "metric": "gdn_decode_gbps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": workload_config(world),
-            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": H2D_BYTES * world,
-                    "d2h_bytes_per_step": D2H_BYTES * world, "ms_per_step": round(e2e_ms / args.steps, 5),
-                    "api": "cuda_extension.gdn_decode_forward"},
-            "gpu_launches": args.steps,
-            "roofline": {"bound": "hbm", "kernel": "gdn_decode_v8_kernel<8>", "achieved": round(per_gpu, 2),
-                         "peak": peak, "unit": "GB/s", "frac": round(per_gpu / peak, 4),
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes": BYTES_PER_STEP,
-                         "peak_source": peak_src},
-            "clocks": sampler.summary(windows),
-        }
-        if graph_ms is not None:
-            line["cuda_graph"] = {"ms_per_step": round(graph_ms, 5), "value": round(BYTES_PER_STEP / graph_ms / 1e6, 2),
-                                  "unit": "GB/s per GPU", "launches_per_graph": N_DISTINCT_STEPS}
-        if world == 1 and not args.no_cpu_baseline:
-            gbs, dt, sample, threads = time_oracle_cpu(n_steps=20, n_warmup=1, budget_s=15.0)
-            line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-                                    "sample": sample, "ms_per_step_sample": round(dt * 1e3, 3)}
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        g = GdnDecodeGraph(wl.state, wl.out, wl.q, wl.k, wl.v, wl.g, wl.beta, args.config)
+        gms, gn = ctx.timed(lambda i: g.replay(), max(1, args.steps // wl.N_DISTINCT), 1)
+        graph = {"ms_per_step": round(gms / wl.N_DISTINCT, 5), "unit": "GB/s per GPU",
+                 "value": round(wl.bytes_per_step / (gms / wl.N_DISTINCT) / 1e6, 2), "launches_per_graph": wl.N_DISTINCT}
+    pipe = wl.make_e2e(args.config)
+    e2e_ms, e2e_n = ctx.timed(None, args.steps, min(args.warmup, 16), run_n=pipe.run)
+    world = ctx.world
+    per_gpu = wl.bytes_per_step / (ms * 1e-3) / 1e9
+    peak = ctx.peaks["hbm_gbs"]
+    kernel = "gdn_decode_v8_kernel<8>"
+    rec = {
+        "metric": "gdn_decode_gbps", "value": round(per_gpu * world, 2), "unit": "GB/s", "n_gpus": world,
+        "steps": n, "steps_requested": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gdn_decode_serving", "B_per_gpu": wl.B, "Hq": wl.HQ, "Hv": wl.HV, "dk": wl.D,
+                   "dv": wl.D, "state_bytes_per_gpu": wl.B * wl.HV * wl.D * wl.D * 4,
+                   "distinct_steps": wl.N_DISTINCT, "bytes_per_step_per_gpu": wl.bytes_per_step,
+                   "parallelism": f"batch-sharded x{world}, no collective",
+                   "l2": "state (512 MiB) exceeds L2 (126 MB); no flush needed",
+                   "min_timed_region_s": args.min_region_s},
+        "e2e": {"value": round(wl.bytes_per_step * world / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": wl.h2d_bytes * world, "d2h_bytes_per_step": wl.d2h_bytes * world,
+                "ms_per_step": round(e2e_ms, 5), "steps": e2e_n, "api": "cuda_extension.gdn_decode_forward",
+                "copies_per_step": "1 host->device (packed q,k,v,g,beta), 1 device->host"},
+        "gpu_launches": n,
+        "roofline": {"bound": "hbm", "kernel": kernel, "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(per_gpu / peak, 4), "traffic": NCU_TRAFFIC[kernel],
+                     "algorithmic_bytes": wl.bytes_per_step, "peak_source": ctx.peaks["source"] + " hbm_gbs"},
+    }
+    if graph:
+        rec["cuda_graph"] = graph
+    if cpu_baseline:
+        gbs, dt, sample, threads = bw.cpu_gdn(budget_s=12.0)
+        rec["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                               "sample": sample, "ms_per_step_sample": round(dt * 1e3, 3)}
+    del wl, pipe
+    torch.cuda.empty_cache()
+    return rec
 
 
-def run_moe(args):
-    """Secondary line: the FP8 MoE layer of 4096 tokens (hidden 2048, intermediate 1024, 64 experts, top-6).
-
-    value = grouped-GEMM FLOP (6*T*k*H*I) / time of the two grouped GEMM kernels; e2e = the same FLOP
-    over the whole layer through cuda_extension.moe_forward with x coming from pinned host memory and
-    the output going back. Weights (403 MB) exceed L2, so no flush is needed between steps."""
-    import torch
-    from cuda_agent_b200.benchmarks import MoeWorkload, time_cuda
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    wl = MoeWorkload(dev)
-    steps, warmup = min(args.steps, 200), max(3, min(args.warmup, 20))
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    w0 = time.monotonic()
-    ms_gemm = time_cuda(lambda: wl.gemm_step(args.config), steps, warmup)
-    ms_layer = time_cuda(lambda: wl.layer_step(config=args.config), steps, warmup)
-    hx = wl.x.cpu().pin_memory()
-    ho = torch.empty_like(hx).pin_memory()
-    dx = torch.empty_like(wl.x)
-
-    def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        ho.copy_(wl.layer_step(dx, args.config), non_blocking=True)
-    ms_e2e = time_cuda(e2e_step, steps, warmup)
-    windows = [(w0, time.monotonic())]
-    sampler.stop()
+def moe_record(ctx: Ctx, cpu_baseline: bool):
+    """FP8 MoE layer of 4096 tokens (H 2048, I 1024, 64 experts, top-6) on one GPU. value = grouped-GEMM FLOP
+    (6*T*k*H*I) / time of the two grouped GEMM kernels; e2e = the same FLOP over the whole layer through
+    cuda_extension.moe_forward with x from pinned host memory and the output back (pipelined)."""
+    import bench_workloads as bw
+    args, torch = ctx.args, ctx.torch
+    wl = bw.MoeWorkload(ctx.dev)
+    steps, warmup = min(args.steps, 200), min(args.warmup, 20)
+    ms_gemm, n = ctx.timed(lambda i: wl.gemm_step(args.config), steps, warmup)
+    ms_layer, _ = ctx.timed(lambda i: wl.layer_step(config=args.config), steps, warmup)
+    pipe = wl.make_e2e(args.config)
+    ms_e2e, n_e2e = ctx.timed(None, steps, 5, run_n=pipe.run)
     assert wl.status.cpu().tolist() == [0, 0]
     tflops = wl.gemm_flops / (ms_gemm * 1e-3) / 1e12
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    if peaks_file.exists():
-        peak = 2.0 * float(json.loads(peaks_file.read_text())["bf16_tflops"])
-        src = "2 x measured bf16 burst (MEASURED_PEAKS.json bf16_tflops); nominal fp8 dense 4500"
-    else:
-        peak, src = 2.0 * 1590.0, "2 x fallback bf16 1590; nominal fp8 dense 4500"
-    line = {
+    peak2 = 2.0 * ctx.peaks["bf16_tflops"]
+    kernel = "moe_gemm_fp8_kernel<0> + <1>"
+    rec = {
         "metric": "moe_fp8_grouped_gemm_tflops", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": 1,
-        "steps": steps, "warmup": warmup, "ms_per_step": round(ms_gemm, 5), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+        "steps": n, "ms_per_step": round(ms_gemm, 5), "higher_is_better": True,
+        "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
         "config": {"workload": "moe_fp8_layer", "T": wl.T, "H": wl.H, "I": wl.I, "E": wl.E, "k": wl.k,
                    "gemm_flops": wl.gemm_flops, "min_bytes": wl.min_bytes,
                    "l2": "expert weights (403 MB) exceed L2 (126 MB); no flush needed"},
         "layer_ms": round(ms_layer, 5),
+        "layer_tflops": round(wl.gemm_flops / (ms_layer * 1e-3) / 1e12, 2),
         "e2e": {"value": round(wl.gemm_flops / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-                "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2,
-                "ms_per_step": round(ms_e2e, 5), "api": "cuda_extension.moe_forward"},
-        "gpu_launches": 2 * steps,
-        "roofline": {"bound": "tensor", "kernel": "moe_gemm_fp8_kernel<0> + <1>", "achieved": round(tflops, 2),
-                     "peak": peak, "unit": "TFLOP/s", "frac": round(tflops / peak, 4), "traffic": None,
-                     "peak_source": src},
-        "clocks": sampler.summary(windows),
+                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
+                "ms_per_step": round(ms_e2e, 5), "steps": n_e2e, "api": "cuda_extension.moe_forward"},
+        "gpu_launches": 2 * n,
+        "roofline": {"bound": "tensor", "kernel": kernel, "achieved": round(tflops, 2), "peak": NOMINAL_FP8_TFLOPS,
+                     "unit": "TFLOP/s", "frac": round(tflops / NOMINAL_FP8_TFLOPS, 4),
+                     "peak_source": "nominal fp8 dense (no measured fp8 figure exists)",
+                     "frac_of_2x_measured_bf16": round(tflops / peak2, 4), "peak_2x_measured_bf16": peak2,
+                     "traffic": NCU_TRAFFIC[kernel]},
     }
-    print(json.dumps(line), flush=True)
+    if cpu_baseline:
+        tf, dt, sample, threads = bw.cpu_moe()
+        rec["cpu_baseline"] = {"value": round(tf, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                               "sample": sample, "s_per_layer": round(dt, 3)}
+    del wl, pipe
+    torch.cuda.empty_cache()
+    return rec
 
 
-def run_mla(args):
-    """Secondary line: sparse MLA decode, 64 sequences x 128 heads, 2048 selected rows of a 2.4 GB cache.
-
-    value = sequences (one new token each) per second with everything in HBM; e2e = the same through
+def mla_record(ctx: Ctx, cpu_baseline: bool):
+    """Sparse MLA decode, 64 sequences x 128 heads per GPU, 2048 selected rows of a 2.4 GB cache. value =
+    sequences (one new token each) per second with everything in HBM; e2e = the same through
     cuda_extension.mla_sparse_decode_forward with q / idx / seq_len from pinned host memory and the output
-    back (the KV cache is resident, as in serving). The cache (2.4 GB) exceeds L2; the 2048 rows a step
-    touches per sequence are 151 MB in total, also above L2, so no flush is needed."""
-    import torch
-    import torch.distributed as dist
-    from cuda_agent_b200.benchmarks import MlaWorkload, time_cuda
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    wl = MlaWorkload(dev, seed=1236 + rank)
-    steps, warmup = min(args.steps, 200), max(3, min(args.warmup, 20))
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    w0 = time.monotonic()
-
-    def timed(fn):
-        """ms per call: CUDA events between barriers, max over ranks."""
-        if world > 1:
-            dist.barrier()
-        t = torch.tensor([time_cuda(fn, steps, warmup)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
-
-    ms = timed(lambda: wl.step(args.nsplit, args.config))
-    hq, hidx, hlen = wl.q.cpu().pin_memory(), wl.idx.cpu().pin_memory(), wl.seq_len.cpu().pin_memory()
-    ho = torch.empty(wl.out.shape, dtype=torch.bfloat16).pin_memory()
-    dq, didx, dlen = torch.empty_like(wl.q), torch.empty_like(wl.idx), torch.empty_like(wl.seq_len)
-
-    def e2e_step():
-        dq.copy_(hq, non_blocking=True); didx.copy_(hidx, non_blocking=True); dlen.copy_(hlen, non_blocking=True)
-        ho.copy_(wl.api_step(dq, didx, dlen), non_blocking=True)
-    ms_e2e = timed(e2e_step)
-    windows = [(w0, time.monotonic())]
-    sampler.stop()
+    back (the KV cache is resident, as in serving)."""
+    import bench_workloads as bw
+    args, torch = ctx.args, ctx.torch
+    wl = bw.MlaWorkload(ctx.dev, seed=1236 + ctx.rank)
+    steps, warmup = min(args.steps, 200), min(args.warmup, 20)
+    nsplit = args.nsplit if args.nsplit > 0 else 1
+    ms, n = ctx.timed(lambda i: wl.step(nsplit, args.config), steps, warmup)
+    pipe = wl.make_e2e(args.nsplit, args.config)
+    ms_e2e, n_e2e = ctx.timed(None, steps, 5, run_n=pipe.run)
     assert int(wl.status) == 0
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank != 0:
-        return
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0}
+    world = ctx.world
+    peaks = ctx.peaks
     t_roof = max(wl.bytes / (peaks["hbm_gbs"] * 1e9), wl.flops / (peaks["bf16_tflops"] * 1e12))
     gbs = wl.bytes / (ms * 1e-3) / 1e9
-    line = {
+    kernel = "mla_sparse_decode_pair_kernel"
+    rec = {
         "metric": "sparse_mla_decode_tok_per_s", "value": round(wl.B * world / (ms * 1e-3), 1), "unit": "tok/s",
-        "n_gpus": world,
-        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16 (fp32 softmax and accumulation)", "data": "synthetic",
+        "n_gpus": world, "steps": n, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak",
+        "dtype": "bf16 (fp32 softmax and accumulation)", "data": "synthetic",
         "config": {"workload": "sparse_mla_decode", "B_per_gpu": wl.B, "heads": wl.Hh, "S": wl.S, "topk": wl.topk,
-                   "nsplit": args.nsplit, "bytes": wl.bytes, "flops": wl.flops,
+                   "nsplit": nsplit, "bytes": wl.bytes, "flops": wl.flops,
+                   "parallelism": f"batch-sharded x{world}, no collective",
                    "l2": "rows touched per step (151 MB) and the cache (2.4 GB) exceed L2; no flush needed"},
         "e2e": {"value": round(wl.B * world / (ms_e2e * 1e-3), 1), "unit": "tok/s",
-                "h2d_bytes_per_step": (hq.numel() * 2 + hidx.numel() * 4 + hlen.numel() * 4) * world,
-                "d2h_bytes_per_step": ho.numel() * 2 * world, "ms_per_step": round(ms_e2e, 5),
-                "api": "cuda_extension.mla_sparse_decode_forward"},
-        "gpu_launches": steps * (1 if args.nsplit == 1 else 2),
-        "roofline": {"bound": "hbm", "kernel": "mla_sparse_decode_pair_kernel", "achieved": round(gbs, 1),
-                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None,
+                "h2d_bytes_per_step": wl.h2d_bytes * world, "d2h_bytes_per_step": wl.d2h_bytes * world,
+                "ms_per_step": round(ms_e2e, 5), "steps": n_e2e, "api": "cuda_extension.mla_sparse_decode_forward"},
+        "gpu_launches": n * (1 if nsplit == 1 else 2),
+        "roofline": {"bound": "hbm", "kernel": kernel, "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC[kernel],
                      "roofline_time_us": round(t_roof * 1e6, 2), "frac_of_roofline_time": round(t_roof / (ms * 1e-3), 4),
-                     "peak_source": "MEASURED_PEAKS.json (hbm_gbs; bf16_tflops for the compute side)"},
-        "clocks": sampler.summary(windows),
+                     "peak_source": peaks["source"] + " hbm_gbs; bf16_tflops for the compute side"},
     }
-    print(json.dumps(line), flush=True)
+    if cpu_baseline:
+        tps, dt, sample, threads = bw.cpu_mla(wl)
+        rec["cpu_baseline"] = {"value": round(tps, 2), "unit": "tok/s", "cores": threads, "kind": "port",
+                               "sample": sample, "s_per_sequence": round(dt, 4)}
+    del wl, pipe
+    torch.cuda.empty_cache()
+    return rec
 
 
-def run_moe_ep(args):
-    """Secondary line: the expert-parallel FP8 MoE layer (8192 tokens per GPU, H 7168, I 2048, 256 experts
-    over the ranks, top-8 group-limited sigmoid routing, one shared expert). Launch with torchrun for N > 1.
-    value = GEMM FLOP of all ranks / max-over-ranks layer time (CUDA events around the whole layer call,
-    all-to-all exchanges included). e2e adds the host round trip of x and the output."""
-    import torch
-    import torch.distributed as dist
-    from cuda_agent_b200.benchmarks import MoeEpWorkload
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    wl = MoeEpWorkload(dev, rank, world, micro_batches=args.micro_batches, gemm_ctas=args.config,
-                       dedup=False if args.no_dedup else None)
-    steps, warmup = min(args.steps, 30), max(3, min(args.warmup, 5))
+def moe_ep_record(ctx: Ctx, cpu_baseline: bool):
+    """Expert-parallel FP8 MoE layer (8192 tokens per GPU, H 7168, I 2048, 256 experts over the ranks, top-8
+    group-limited sigmoid routing, one shared expert). value = GEMM FLOP of all ranks / max-over-ranks layer
+    time (CUDA events around the whole layer call, exchanges included). e2e adds the host round trip of x and
+    the output (pipelined)."""
+    import bench_workloads as bw
+    args, torch = ctx.args, ctx.torch
+    wl = bw.MoeEpWorkload(ctx.dev, ctx.rank, ctx.world, mode=args.ep_mode)
+    steps, warmup = min(args.steps, 30), min(args.warmup, 5)
+    out = wl.step()
+    torch.cuda.synchronize()
+    parity = wl.parity(out) if ctx.rank == 0 else None
+    del out
+    ctx.barrier()
+    ms, n = ctx.timed(lambda i: wl.step(), steps, warmup)
+    pipe = wl.make_e2e()
+    ms_e2e, n_e2e = ctx.timed(None, steps, 3, run_n=pipe.run)
+    status = wl.layer.status_codes()
+    assert not any(status), f"a kernel of the layer gave up a bounded wait or flagged its input: {status}"
+    world = ctx.world
+    tflops = wl.flops_per_gpu * world / (ms * 1e-3) / 1e12
+    peak2 = 2.0 * ctx.peaks["bf16_tflops"]
+    rec = {
+        "metric": "moe_ep_fp8_layer_tflops", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": n, "ms_per_step": round(ms, 4), "layer_ms_max_over_ranks": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
+        "config": {"workload": "moe_ep_layer", "T_per_gpu": wl.T, "H": wl.H, "I": wl.I, "E": wl.E, "k": wl.k,
+                   "experts_per_gpu": wl.E // world, "shared_experts": 1, "flops_per_gpu": wl.flops_per_gpu,
+                   "parallelism": f"ep{world}, " + wl.layer.describe(),
+                   "l2": "expert weights (>= 1.4 GB per GPU) exceed L2; no flush needed"},
+        "parity": {"rel_l2": None if parity is None else round(parity, 5), "tolerance": 2e-2, "tokens": 256,
+                   "against": "oracle/moe/model.py functions on rank 0's first 256 tokens, on the GPU, untimed"},
+        "e2e": {"value": round(wl.flops_per_gpu * world / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": wl.h2d_bytes * world, "d2h_bytes_per_step": wl.d2h_bytes * world,
+                "ms_per_step": round(ms_e2e, 4), "steps": n_e2e, "api": "cuda_agent_b200.ep layer.forward"},
+        "gpu_launches": n * wl.layer.launches_per_call(),
+        "roofline": {"bound": "tensor", "kernel": "moe_gemm_fp8_kernel (layer time incl. exchanges)",
+                     "achieved": round(tflops / world, 2), "peak": NOMINAL_FP8_TFLOPS, "unit": "TFLOP/s",
+                     "frac": round(tflops / world / NOMINAL_FP8_TFLOPS, 4),
+                     "peak_source": "nominal fp8 dense, per GPU",
+                     "frac_of_2x_measured_bf16": round(tflops / world / peak2, 4), "traffic": None},
+    }
+    if parity is not None:
+        assert parity <= 2e-2, f"expert-parallel layer off the oracle: rel-L2 {parity}"
+    if cpu_baseline:
+        tf, dt, sample, threads = bw.cpu_moe_ep()
+        rec["cpu_baseline"] = {"value": round(tf, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                               "sample": sample, "s_sample": round(dt, 3),
+                               "s_per_layer_extrapolated": round(wl.flops_per_gpu / (tf * 1e12), 2)}
+    wl.layer.close()
+    del wl, pipe
+    torch.cuda.empty_cache()
+    return rec
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
 
-    def timed(fn):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
+RECORDS = {"gdn": gdn_record, "moe": moe_record, "mla": mla_record, "moe_ep": moe_ep_record}
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    w0 = time.monotonic()
-    ms = timed(wl.step)
-    hx = wl.x.cpu().pin_memory()
-    ho = torch.empty_like(hx).pin_memory()
-    dx = torch.empty_like(wl.x)
 
-    def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        ho.copy_(wl.step(dx), non_blocking=True)
-    ms_e2e = timed(e2e_step)
-    windows = [(w0, time.monotonic())]
-    sampler.stop()
-    assert wl.ops.status.cpu().tolist() == [0, 0, 0, 0]
-    if rank == 0:
-        tflops = wl.flops_per_gpu * world / (ms * 1e-3) / 1e12
-        peaks_file = ROOT / "MEASURED_PEAKS.json"
-        peak = 2.0 * (float(json.loads(peaks_file.read_text())["bf16_tflops"]) if peaks_file.exists() else 1590.0)
-        line = {
-            "metric": "moe_ep_fp8_layer_tflops", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": world,
-            "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32", "data": "synthetic",
-            "config": {"workload": "moe_ep_layer", "T_per_gpu": wl.T, "H": wl.H, "I": wl.I, "E": wl.E, "k": wl.k,
-                       "experts_per_gpu": wl.E // world, "shared_experts": 1, "flops_per_gpu": wl.flops_per_gpu,
-                       "parallelism": f"ep{world}, NCCL all-to-all dispatch/return",
-                       "l2": "expert weights (>= 1.4 GB per GPU) exceed L2; no flush needed"},
-            "e2e": {"value": round(wl.flops_per_gpu * world / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": hx.numel() * 2 * world, "d2h_bytes_per_step": ho.numel() * 2 * world,
-                    "ms_per_step": round(ms_e2e, 4), "api": "cuda_agent_b200.ep.ep_moe_forward"},
-            "gpu_launches": steps * 14,
-            "roofline": {"bound": "tensor", "kernel": "moe_gemm_fp8_kernel (layer time incl. exchanges)",
-                         "achieved": round(tflops / world, 2), "peak": peak, "unit": "TFLOP/s",
-                         "frac": round(tflops / world / peak, 4), "traffic": None,
-                         "peak_source": "2 x measured bf16 burst; per GPU"},
-            "clocks": sampler.summary(windows),
-        }
+def run_b200(args):
+    from cuda_agent_b200 import capi, load_extension
+    load_extension()
+    capi.lib()
+    ctx = Ctx(args)
+    cpu = ctx.world == 1 and not args.no_cpu_baseline
+    head = "gdn" if args.workload == "all" else args.workload
+    if head == "moe" and ctx.world > 1:
+        raise SystemExit("bench.py: --workload moe is the one-GPU layer; the expert-parallel one is moe_ep")
+    line = RECORDS[head](ctx, cpu)
+    line.setdefault("n_gpus", ctx.world)
+    line.setdefault("scaling", "weak")
+    line.setdefault("vs_baseline", None)
+    line.setdefault("warmup", max(3, args.warmup))
+    if args.workload == "all":
+        sec = {}
+        if ctx.world == 1:
+            sec["moe"] = moe_record(ctx, cpu)
+        sec["mla"] = mla_record(ctx, cpu)
+        sec["moe_ep"] = moe_ep_record(ctx, cpu)
+        line["secondary"] = sec
+        line["gpu_launches"] += sum(r["gpu_launches"] for r in sec.values())
+    line["clocks"] = ctx.finish()
+    if ctx.rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    """The eager oracles on all host cores (the reference's torch-eager CPU path for these operators; kind
+    "port" because the reference ships no implementation of them). Rank 0 only. The figures are rates of one
+    host: they stand for one box's CPU whatever --gpus says."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import bench_workloads as bw
+    which = args.workload
+    secondary = {}
+
+    def gdn():
+        gbs, dt, sample, threads = bw.cpu_gdn(budget_s=60.0 if which == "all" else 150.0,
+                                              n_steps=min(args.steps, 20), n_warmup=max(1, min(args.warmup, 2)))
+        return {"metric": "gdn_decode_gbps", "value": round(gbs, 3), "unit": "GB/s", "ms_per_step": round(dt * 1e3, 4),
+                "dtype": "f32", "config": {"workload": "gdn_decode_serving", "B_per_gpu": 256, "Hq": 16, "Hv": 32,
+                                            "dk": 128, "dv": 128},
+                "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample}}
+
+    def moe():
+        tf, dt, sample, threads = bw.cpu_moe()
+        return {"metric": "moe_fp8_grouped_gemm_tflops", "value": round(tf, 4), "unit": "TFLOP/s",
+                "ms_per_step": round(dt * 1e3, 2), "dtype": "f32 on dequantised e4m3",
+                "config": {"workload": "moe_fp8_layer", "T": 4096, "H": 2048, "I": 1024, "E": 64, "k": 6},
+                "cpu_baseline": {"value": round(tf, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}}
+
+    def mla():
+        import torch
+
+        class HostInputs:          # the oracle's own generator at the workload's shapes, 16 sequences
+            pass
+        m = bw.load_oracle("mla", {"CAB_MLA_CONFIG": 2})
+        gen = torch.Generator().manual_seed(1236)
+        n_seq = 16
+        q, kv, seq_len, idx = m.make_inputs(n_seq, 128, 32768, 2048, 8192, gen)
+        wl = HostInputs()
+        wl.q, wl.kv, wl.seq_len, wl.idx, wl.Hh, wl.S, wl.topk = q, kv, seq_len, idx, 128, 32768, 2048
+        tps, dt, sample, threads = bw.cpu_mla(wl, n_seq)
+        return {"metric": "sparse_mla_decode_tok_per_s", "value": round(tps, 2), "unit": "tok/s",
+                "ms_per_step": round(dt * 64 * 1e3, 2), "dtype": "f32 from bf16",
+                "config": {"workload": "sparse_mla_decode", "B_per_gpu": 64, "heads": 128, "S": 32768, "topk": 2048},
+                "cpu_baseline": {"value": round(tps, 2), "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample}}
+
+    def moe_ep():
+        tf, dt, sample, threads = bw.cpu_moe_ep()
+        flops = 6 * 8192 * 8 * 7168 * 2048 + 6 * 8192 * 7168 * 2048
+        return {"metric": "moe_ep_fp8_layer_tflops", "value": round(tf, 4), "unit": "TFLOP/s",
+                "ms_per_step": round(flops / (tf * 1e12) * 1e3, 1), "dtype": "f32 on dequantised e4m3",
+                "config": {"workload": "moe_ep_layer", "T_per_gpu": 8192, "H": 7168, "I": 2048, "E": 256, "k": 8},
+                "cpu_baseline": {"value": round(tf, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}}
+
+    fns = {"gdn": gdn, "moe": moe, "mla": mla, "moe_ep": moe_ep}
+    line = fns["gdn" if which == "all" else which]()
+    if which == "all":
+        for name in ("moe", "mla", "moe_ep"):
+            secondary[name] = fns[name]()
+            secondary[name]["e2e"] = {"value": secondary[name]["value"], "unit": secondary[name]["unit"],
+                                      "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    line.update({
+        "impl": "reference", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+        "e2e": {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "stands_for": "the rate of this one host's CPU cores; it does not grow with n_gpus",
+    })
+    if secondary:
+        line["secondary"] = secondary
+    print(json.dumps(line), flush=True)
 
 
 def main():
     args = parse_args()
-    if args.workload == "moe_ep" and args.impl != "reference":
-        return run_moe_ep(args)
-    if args.workload == "moe" and args.impl != "reference":
-        return run_moe(args)
-    if args.workload == "mla" and args.impl != "reference":
-        return run_mla(args)
     if args.impl == "reference":
         run_reference(args)
     else:

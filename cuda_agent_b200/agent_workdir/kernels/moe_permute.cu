@@ -138,7 +138,7 @@ moe_count_scan_kernel(const int* __restrict__ idx, int n, int E, int nchunks,
 __global__ void __launch_bounds__(kChunk)
 moe_rank_kernel(const int* __restrict__ idx, int n, int E, const int* __restrict__ chunk_base,
                 const int* __restrict__ offsets, const int* __restrict__ pad_offsets,
-                int* __restrict__ perm, int* __restrict__ inv_perm, int* __restrict__ dst_row) {
+                int* __restrict__ perm, int* __restrict__ inv_perm, int* __restrict__ dst_row, int max_rows) {
   __shared__ int wc[32][kMaxE];
   int my_e, rank;
   bool bad;
@@ -157,7 +157,9 @@ moe_rank_kernel(const int* __restrict__ idx, int n, int E, const int* __restrict
     const int pos = __ldg(offsets + my_e) + within;
     inv_perm[i] = pos;
     perm[pos] = i;
-    dst_row[i] = __ldg(pad_offsets + my_e) + within;
+    // rows past the tile table's capacity (flagged as overflow by the count kernel) belong to no tile
+    const int row = __ldg(pad_offsets + my_e) + within;
+    dst_row[i] = row < max_rows ? row : -1;
   } else {
     // a skipped entry has no row: the quantise-dispatch and combine kernels pass over negative rows
     inv_perm[i] = -1;
@@ -338,7 +340,8 @@ extern "C" int moe_permute_launcher(const int* topk_idx, int T, int k, int E, in
                                                         num_tiles, max_tiles, status, (config & 1) != 0);
   if (n > 0)
     moe_rank_kernel<<<nchunks, kChunk, 0, stream>>>(topk_idx, (int)n, E, chunk_cnt, offsets,
-                                                    pad_offsets, perm, inv_perm, dst_row);
+                                                    pad_offsets, perm, inv_perm, dst_row,
+                                                    max_tiles > (1 << 24) ? 0x7fffffff : max_tiles * kTileM);
   return cab::launch_status();
 }
 

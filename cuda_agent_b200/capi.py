@@ -38,7 +38,30 @@ SIGNATURES = {
     "mla_sparse_decode_noalloc_launcher": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p, c_int, c_void_p]),
     "mla_gather_rows_launcher": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p]),
     "moe_grouped_gemm_fp8_launcher": (c_int, [c_int] + [c_void_p] * 8 + [c_int] * 6 + [c_void_p, c_int, c_void_p]),
+    "moe_ep_peer_buffer_bytes": (c_size_t, [c_int] * 4),
+    "moe_ep_peer_create": (c_int, [c_void_p] + [c_int] * 6),
+    "moe_ep_peer_export": (c_int, [c_void_p, c_void_p]),
+    "moe_ep_peer_connect_ipc": (c_int, [c_void_p, c_void_p]),
+    "moe_ep_peer_connect_local": (c_int, [c_void_p, c_void_p]),
+    "moe_ep_peer_destroy": (c_int, [c_void_p]),
+    "moe_ep_peer_dispatch_launcher": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p]),
+    "moe_ep_peer_receive_launcher": (c_int, [c_void_p, c_int, c_void_p]),
+    "moe_ep_peer_gather_launcher": (c_int, [c_void_p] * 4 + [c_int, c_int, c_void_p]),
+    "moe_ep_peer_return_launcher": (c_int, [c_void_p] * 3 + [c_int, c_void_p]),
+    "moe_ep_peer_combine_launcher": (c_int, [c_void_p] * 3 + [c_int, c_int, c_void_p]),
+    "moe_ep_peer_workspace_bytes": (c_size_t, [c_void_p, c_void_p]),
+    "moe_ep_peer_layer_launcher": (c_int, [c_void_p] * 3 + [c_int, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "moe_ep_peer_read_status": (c_int, [c_void_p] * 4),
+    "moe_ep_peer_debug_read": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_size_t]),
 }
+
+
+class MoeEpLayerArgs(ctypes.Structure):
+    """`cab_moe_ep_layer_args` of the header, field for field."""
+    _fields_ = [(n, c_void_p) for n in ("router_w", "router_bias", "w13_q", "w13_s", "w2_q", "w2_s", "shared_w13_q",
+                                        "shared_w13_s", "shared_w2_q", "shared_w2_s")] + \
+               [("E", c_int), ("I", c_int), ("routing", c_int), ("n_group", c_int), ("topk_group", c_int),
+                ("scaling", c_float), ("entry_cap", c_int), ("gemm_ctas", c_int)]
 
 
 class CabError(RuntimeError):

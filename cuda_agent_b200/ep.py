@@ -403,3 +403,159 @@ class CudaOps:
         out = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.dev)
         self.capi.moe_combine(out, y_back, inv_perm, w, shared)
         return out
+
+
+class PeerLayer:
+    """The layer with its exchanges done by the kernels themselves over peer memory (`moe_ep_peer_*` in the
+    C ABI): a token's quantised row is stored straight into the receive buffer of every rank that holds one
+    of its experts, and the weighted partial results are stored straight back. Capacities are fixed when the
+    object is built, so `forward` allocates only its output and never synchronises with the host.
+
+    One process per GPU: the ranks exchange 64-byte CUDA IPC handles of their exchange buffers through
+    `group` (a torch.distributed group; any backend that moves bytes). Several ranks of ONE process (tests
+    on a single GPU, or one process driving several GPUs) are built with `PeerLayer.build_local`."""
+
+    def __init__(self, ops: CudaOps, rank: int, world: int, t_cap: int, group=None, entry_cap=None, _connect=True):
+        import ctypes
+        from . import capi
+        self.ops, self.rank, self.world, self.t_cap = ops, rank, world, t_cap
+        self.capi, self.lib = capi, capi.lib()
+        assert ops.E % world == 0 and ops.e_local == ops.E // world
+        # entries this rank can receive per call: everything when alone, else 1.5 x the balanced share
+        self.entry_cap = entry_cap or (t_cap * ops.k if world == 1 else (t_cap * ops.k * 3) // 2)
+        self.ctx = ctypes.c_void_p()
+        with torch.cuda.device(ops.dev):
+            capi._check("moe_ep_peer_create",
+                        self.lib.moe_ep_peer_create(ctypes.byref(self.ctx), rank, world, t_cap, ops.H, ops.k,
+                                                    ops.e_local))
+        sh = ops.shared or (None, None, None, None)
+        p = lambda t: None if t is None else t.data_ptr()
+        self.args = capi.MoeEpLayerArgs(p(ops.router_w), p(ops.router_bias), p(ops.w13_q), p(ops.w13_s), p(ops.w2_q),
+                                        p(ops.w2_s), p(sh[0]), p(sh[1]), p(sh[2]), p(sh[3]), ops.E, ops.I, ops.routing,
+                                        ops.n_group, ops.topk_group, float(ops.scaling), self.entry_cap, ops.gemm_ctas)
+        nbytes = self.lib.moe_ep_peer_workspace_bytes(self.ctx, ctypes.byref(self.args))
+        if nbytes == 0:
+            raise ValueError("moe_ep_peer_workspace_bytes rejected the layer's shapes")
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=ops.dev)
+        if _connect:
+            self._connect_ipc(group)
+
+    def _connect_ipc(self, group):
+        import ctypes
+        mine = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.ops.dev):
+            self.capi._check("moe_ep_peer_export", self.lib.moe_ep_peer_export(self.ctx, mine))
+        if self.world == 1:
+            handles = bytes(mine)
+        else:
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, bytes(mine), group=group)
+            handles = b"".join(gathered)
+        with torch.cuda.device(self.ops.dev):
+            self.capi._check("moe_ep_peer_connect_ipc", self.lib.moe_ep_peer_connect_ipc(self.ctx, handles))
+
+    @staticmethod
+    def build_local(ops_per_rank, t_cap: int, entry_cap=None):
+        """All ranks inside this process (each `ops` on its own device, or all on one)."""
+        import ctypes
+        world = len(ops_per_rank)
+        layers = [PeerLayer(o, r, world, t_cap, entry_cap=entry_cap, _connect=False) for r, o in enumerate(ops_per_rank)]
+        table = (ctypes.c_void_p * world)(*[l.ctx.value for l in layers])
+        for l in layers:
+            with torch.cuda.device(l.ops.dev):
+                l.capi._check("moe_ep_peer_connect_local", l.lib.moe_ep_peer_connect_local(l.ctx, table))
+        return layers
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor = None, stages: int = 0) -> torch.Tensor:
+        """One layer call. `stages` (bit 0: routing + dispatch + shared expert, bit 1: receive + GEMMs + return,
+        bit 2: combine; 0 = all) is for ranks that share one GPU, which are stepped stage by stage."""
+        import ctypes
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty(T, self.ops.H, dtype=torch.bfloat16, device=x.device)
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        with torch.cuda.device(x.device):
+            self.capi._check("moe_ep_peer_layer_launcher",
+                             self.lib.moe_ep_peer_layer_launcher(self.ctx, out.data_ptr(), x.data_ptr(), T,
+                                                                 ctypes.byref(self.args), self.workspace.data_ptr(),
+                                                                 self.workspace.numel(), stages, stream))
+        return out
+
+    @staticmethod
+    def forward_local(layers, xs):
+        """One layer call of every rank of `build_local`, stage by stage; returns the outputs in rank order."""
+        outs = [torch.empty(x.shape[0], l.ops.H, dtype=torch.bfloat16, device=x.device) for l, x in zip(layers, xs)]
+        for stage in (1, 2, 4):
+            for l, x, o in zip(layers, xs, outs):
+                l.forward(x, o, stage)
+        return outs
+
+    def status_codes(self) -> list:
+        import ctypes
+        host = (ctypes.c_int * 8)()
+        with torch.cuda.device(self.ops.dev):
+            self.capi._check("moe_ep_peer_read_status",
+                             self.lib.moe_ep_peer_read_status(self.ctx, ctypes.byref(self.args),
+                                                              self.workspace.data_ptr(), host))
+        return list(host)
+
+    def debug_read(self, which: int, numel: int, dtype, offset_bytes: int = 0) -> torch.Tensor:
+        out = torch.empty(numel, dtype=dtype, device=self.ops.dev)
+        with torch.cuda.device(self.ops.dev):
+            self.capi._check("moe_ep_peer_debug_read",
+                             self.lib.moe_ep_peer_debug_read(self.ctx, which, offset_bytes, out.data_ptr(),
+                                                             out.numel() * out.element_size()))
+        return out
+
+    def describe(self) -> str:
+        return ("rows stored into the peers' receive buffers by the dispatch kernel and partial results stored back "
+                "by the return kernel (peer memory over NVLink, release/acquire flags, no collective call, no host sync)")
+
+    def launches_per_call(self) -> int:
+        return 17 + (3 if self.ops.shared is not None else 0)
+
+    def close(self) -> None:
+        if self.ctx:
+            with torch.cuda.device(self.ops.dev):
+                self.lib.moe_ep_peer_destroy(self.ctx)
+            self.ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class NcclLayer:
+    """The layer with its exchanges made by NCCL all-to-all calls (`ep_moe_forward`): the baseline form."""
+
+    def __init__(self, ops: CudaOps, world: int, group=None, dedup=None, micro_batches: int = 1):
+        self.ops, self.world, self.group, self.dedup, self.micro_batches = ops, world, group, dedup, micro_batches
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ep_moe_forward(x, self.ops, self.world, self.group, self.micro_batches, self.dedup)
+
+    def status_codes(self) -> list:
+        return self.ops.status.cpu().tolist()
+
+    def describe(self) -> str:
+        return "NCCL all-to-all dispatch/return, one copy of a token per destination rank"
+
+    def launches_per_call(self) -> int:
+        return 14
+
+    def close(self) -> None:
+        pass
+
+
+def make_layer(ops: CudaOps, rank: int, world: int, t_cap: int, mode: str = "peer", group=None):
+    """The expert-parallel layer object for this rank: `.forward(x)` runs one layer call.
+
+    mode "peer": rows are pushed into the other ranks' receive buffers by the kernels themselves
+    (`PeerLayer`); mode "nccl": the exchanges are NCCL all-to-all calls (`NcclLayer`)."""
+    if mode == "nccl":
+        return NcclLayer(ops, world, group)
+    if mode == "peer":
+        return PeerLayer(ops, rank, world, t_cap, group)
+    raise ValueError(f"unknown expert-parallel mode {mode!r}")

@@ -215,6 +215,92 @@ int moe_grouped_gemm_fp8_launcher(int mode, void* out, float* out_scales_t, cons
                                   int config, cab_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
+/* Expert-parallel MoE layer whose dispatch and return are done by the kernels   */
+/* themselves over peer memory (NVLink). The reference ships no such op; the     */
+/* launchers keep the ABI of agent_workdir/kernels/axpby.cu:12-20 and add what a  */
+/* multi-GPU op needs: a context object that owns this rank's exchange buffer.    */
+/* Ranks: expert e lives on rank e / (E / world). One process per GPU exchanges    */
+/* 64-byte handles (moe_ep_peer_export / _connect_ipc: CUDA IPC); several ranks     */
+/* inside one process connect with moe_ep_peer_connect_local.                      */
+/*                                                                                 */
+/* moe_ep_peer_create allocates (cudaMalloc, once) the exchange buffer of           */
+/* moe_ep_peer_buffer_bytes(world, t_cap, H, k) bytes plus small tables, on the     */
+/* current device. t_cap bounds the tokens per rank and call; every capacity is     */
+/* fixed here, so a layer call allocates nothing and never synchronises with the    */
+/* host. H % 256 == 0, k <= 32, world <= 16, e_local = experts on each rank <= 256.  */
+/* All ranks must make the same sequence of layer calls.                           */
+/* ------------------------------------------------------------------------- */
+size_t moe_ep_peer_buffer_bytes(int world, int t_cap, int H, int k);
+int moe_ep_peer_create(void** ctx_out, int rank, int world, int t_cap, int H, int k, int e_local);
+int moe_ep_peer_export(void* ctx, void* handle64);                 /* writes 64 bytes */
+int moe_ep_peer_connect_ipc(void* ctx, const void* handles);       /* world x 64 bytes, in rank order */
+int moe_ep_peer_connect_local(void* ctx, void* const* all_ctx);    /* world contexts of this process, in rank order */
+int moe_ep_peer_destroy(void* ctx);
+
+/* The stages of one layer call (moe_ep_peer_layer_launcher runs them in order):   */
+/*  dispatch: per destination rank, every local token with an expert there gets a   */
+/*    row; the token is quantised 1x128 e4m3 once and stored, with its scales and    */
+/*    its k (weight, local expert | -1) slots, into that rank's receive buffer;      */
+/*    then the number of rows sent is published to every rank.                       */
+/*  receive: waits (bounded, about 3 s) until every rank has published, then         */
+/*    derives the sort keys (local expert per slot, -1 = none) of everything received.*/
+/*  gather: copies received rows to dst_row[(source*t_cap + row)*k + slot] of a_q      */
+/*    (scales transposed to a_scales_t[block*ld_rows + row]); dst_row comes from       */
+/*    moe_permute_launcher on the keys with config 1.                                  */
+/*  return: per received row, sum over its slots of weight * y[dst_row] (fp32 -> bf16) */
+/*    stored into the sending rank's return buffer; then published to every rank.      */
+/*  combine: waits (bounded) for every rank's return, then out[t] = sum of the          */
+/*    partial rows of token t (+ shared[t]).                                           */
+int moe_ep_peer_dispatch_launcher(void* ctx, const cab_bf16* x, const int* topk_idx, const float* topk_w, int T,
+                                  int config, cab_stream_t stream);
+int moe_ep_peer_receive_launcher(void* ctx, int config, cab_stream_t stream);
+int moe_ep_peer_gather_launcher(void* ctx, cab_e4m3* a_q, float* a_scales_t, const int* dst_row, int ld_rows,
+                                int config, cab_stream_t stream);
+int moe_ep_peer_return_launcher(void* ctx, const cab_bf16* y, const int* dst_row, int config, cab_stream_t stream);
+int moe_ep_peer_combine_launcher(void* ctx, cab_bf16* out, const cab_bf16* shared, int T, int config,
+                                 cab_stream_t stream);
+
+/* Weights and routing rule of the layer on this rank (device pointers).           */
+typedef struct cab_moe_ep_layer_args {
+  const cab_bf16* router_w;        /* [E, H] */
+  const float* router_bias;        /* [E] (routing 1) or NULL */
+  const cab_e4m3* w13_q;           /* [e_local, 2I, H] this rank's experts */
+  const float* w13_s;              /* [e_local, 2I/128, H/128] */
+  const cab_e4m3* w2_q;            /* [e_local, H, I] */
+  const float* w2_s;               /* [e_local, H/128, I/128] */
+  const cab_e4m3* shared_w13_q;    /* [2I, H] shared expert, or all four NULL */
+  const float* shared_w13_s;
+  const cab_e4m3* shared_w2_q;
+  const float* shared_w2_s;
+  int E;                           /* experts over all ranks = e_local * world */
+  int I;                           /* expert intermediate size, % 128 == 0 */
+  int routing;                     /* 0 softmax top-k, 1 sigmoid + bias + groups */
+  int n_group, topk_group;
+  float scaling;                   /* routed scaling factor */
+  int entry_cap;                   /* (token, expert) entries this rank can receive per call */
+  int gemm_ctas;                   /* 0 = one persistent GEMM CTA per SM */
+} cab_moe_ep_layer_args;
+
+/* One layer call: routing, dispatch, grouped GEMMs on the local experts, return,   */
+/* combine, with the shared expert on a side stream of the context. `workspace`:     */
+/* moe_ep_peer_workspace_bytes() bytes of device memory, 256-byte aligned, contents   */
+/* irrelevant, reusable by the next call on the same stream. out: bf16 [T, H].        */
+/* Entries beyond entry_cap are dropped and flagged (status word 4 = 2).              */
+/* config: 0 runs the whole call. Bits select stages (1: routing, dispatch, shared     */
+/* expert; 2: receive, GEMMs, return; 4: combine) for callers that step several ranks   */
+/* living on ONE GPU: there every rank must finish a stage before any rank starts the    */
+/* next, because a launch must never wait for a later launch of the same GPU.            */
+size_t moe_ep_peer_workspace_bytes(void* ctx, const cab_moe_ep_layer_args* args);
+int moe_ep_peer_layer_launcher(void* ctx, cab_bf16* out, const cab_bf16* x, int T, const cab_moe_ep_layer_args* args,
+                               void* workspace, size_t workspace_bytes, int config, cab_stream_t stream);
+/* Blocking: host_out8[0..3] give-up codes of the four GEMM launches, [4] permutation */
+/* flag, [5] 301 if the wait for dispatches ran out, [6] 302 if the wait for returns.  */
+int moe_ep_peer_read_status(void* ctx, const cab_moe_ep_layer_args* args, void* workspace, int* host_out8);
+/* Blocking copy out of the context's buffers, for tests: which = 0 received rows,     */
+/* 1 side band, 2 returned rows, 3 sort keys, 4 rows received per source, 5 copy rows.  */
+int moe_ep_peer_debug_read(void* ctx, int which, size_t offset, void* dst, size_t bytes);
+
+/* ------------------------------------------------------------------------- */
 /* Top-k sparse MLA decode attention (absorbed latent attention, one query      */
 /* token per sequence). The reference ships no such op; these launchers fill     */
 /* the kernel slot of agent_workdir/kernels/ (ABI of axpby.cu:12-20).            */

@@ -27,4 +27,4 @@ def test_reference_style_single_load_build(tmp_path):
                             "import torch, cuda_extension as e; print(sorted(e.registered_ops()))"],
                            cwd=wd, capture_output=True, text=True, timeout=300)
     assert probe.returncode == 0, probe.stderr
-    assert "['axpby', 'gdn_decode', 'mla', 'moe']" in probe.stdout
+    assert "['axpby', 'gdn_decode', 'mla', 'moe', 'moe_ep']" in probe.stdout
