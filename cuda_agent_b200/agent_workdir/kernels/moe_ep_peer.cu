@@ -668,6 +668,9 @@ extern "C" int moe_ep_peer_layer_launcher(void* ctx, cab_bf16* out, const cab_bf
   const int stages = (config & 7) ? (config & 7) : 7;
 
   if (stages & 1) {
+    // the four GEMM status words start at zero (a launch that runs clears its own; the shared expert's
+    // two stay untouched when there is none)
+    if (cudaMemsetAsync(w.status, 0, 8 * sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
     // routing of the local tokens
     EP_TRY(moe_router_logits_launcher(w.logits, x, a->router_w, T, H, a->E, 0, stream));
     if (a->routing == 0)
