@@ -247,29 +247,37 @@ class MoeEpWorkload:
                         lambda o, s: ho[s].copy_(o, non_blocking=True))
 
     def parity(self, out, n_tokens=256):
-        """Checker leg (outside every timed region): rel-L2 of `out` on the first n_tokens local tokens against
-        the eager oracle's own functions run on this GPU, with every touched expert's weights drawn again."""
+        """Checker leg (outside every timed region): `out` on the first n_tokens local tokens against the eager
+        oracle's own functions run on this GPU, with every touched expert's weights drawn again. Returns
+        rel_l2 over all those tokens, the number of tokens whose expert set differs from the oracle's (its
+        logits are cuBLAS sums in another order, so a near-tie may fall the other way) and rel_l2 over the
+        tokens routed identically."""
         m = load_oracle("moe", {"CAB_MOE_CONFIG": 4})
         x = self.x[:n_tokens]
         with torch.no_grad():
             logits = x.float() @ self.router_w.float().t()
             idx, w = m.route_sigmoid_group_topk(logits, self.router_bias, self.k, 8, 4, 1.0)
+            got_idx, _ = self.ops.route(x.contiguous())
+            same = (got_idx == idx).all(dim=1)
             xq, sx = m.quant_1x128(x.float())
-            ref = torch.zeros(n_tokens, self.H, device=self.dev)
-            # slot order of the weighted sum is ascending per token; entries are visited expert by expert and
-            # added into per-slot partial buffers first so that the order of the final sum is the oracle's
+            # every entry's FFN output rounded to bf16, then the weighted sum in ascending slot order, as the
+            # oracle's Model.forward forms it
             y_slots = torch.zeros(n_tokens, self.k, self.H, dtype=torch.bfloat16, device=self.dev)
             for e in torch.unique(idx).tolist():
                 tok, slot = torch.nonzero(idx == e, as_tuple=True)
                 w13_q, w13_s, w2_q, w2_s = expert_weights(self.dev, self.seed, e, self.H, self.I)
                 y_slots[tok, slot] = m.expert_ffn(xq[tok], sx[tok], w13_q, w13_s, w2_q, w2_s).to(torch.bfloat16)
+            ref = torch.zeros(n_tokens, self.H, device=self.dev)
             for s in range(self.k):
                 ref = ref + w[:, s, None] * y_slots[:, s].float()
             sh = expert_weights(self.dev, self.seed, self.SHARED_ID, self.H, self.I)
             ref = ref + m.expert_ffn(xq, sx, *sh).to(torch.bfloat16).float()
             ref = ref.to(torch.bfloat16).float()
         got = out[:n_tokens].float()
-        return float((got - ref).norm() / ref.norm())
+        rel = lambda a, b: float((a - b).norm() / b.norm())
+        return {"rel_l2": round(rel(got, ref), 5), "tokens": n_tokens,
+                "tokens_routed_differently": int((~same).sum()),
+                "rel_l2_identically_routed": round(rel(got[same], ref[same]), 5)}
 
 
 # --------------------------------------------------------------------------------------------- sparse MLA
