@@ -24,6 +24,7 @@
 #include "cab_common.cuh"
 #include "sm100_primitives.cuh"
 
+#include <cstring>
 #include <mutex>
 
 namespace {
@@ -594,8 +595,70 @@ __device__ __forceinline__ void pair_produce(const MlaParams& p, PairControl& ct
   }
 }
 
+// The same with TMA row gathers (cp.async.bulk.tensor ... tile::gather4): one instruction fetches this CTA's
+// 128-byte (or, for the rotary tile, 64-byte) piece of four selected rows straight into its place in the
+// swizzled tile. Warp pw still owns rows [16 pw, +16) of every block: lanes 0..19 issue one gather each
+// (tile = lane / 4: four value tiles and the rotary tile; four rows = 4 (lane % 4) .. +3), lane 0 posts the
+// bytes the warp's gathers will deliver on the stage's two barriers. Nothing passes through registers and no
+// thread waits for the data.
+__device__ __forceinline__ void pair_produce_tma(const MlaParams& p, PairControl& ctl, uint8_t* kv_tile, int pw,
+                                                 int lane, int b, int j0, int nb, int len, int rank,
+                                                 const CUtensorMap* map_v, const CUtensorMap* map_r) {
+  volatile int* abort_flag = &ctl.abort_flag;
+  const int* idx_b = p.idx + (size_t)b * p.topk;
+  const int seq = b / p.Sq;                                   // b: (sequence, query token)
+  const int row_base = seq * p.S;                             // the cache as one [B * S, 576] tensor
+  const uint8_t* kv_b = reinterpret_cast<const uint8_t*>(p.kv + (size_t)seq * p.S * kDqk);
+  const int vbyte0 = rank * 512, rbyte0 = 1024 + rank * 64;
+  constexpr int kPrefetchAhead = 4;
+  auto entry = [&](int j) {
+    const int i = (j0 + j) * kTok + pw * 16 + (lane & 15);
+    return (j < nb && i < p.topk) ? __ldg(idx_b + i) : -1;
+  };
+  auto prefetch = [&](int t) {
+    if (lane < 16 && t >= 0 && t < len) {
+      const uint8_t* row = kv_b + (size_t)t * (kDqk * 2);
+#pragma unroll
+      for (int l = 0; l < 4; ++l) sm100::prefetch_l2_line(row + vbyte0 + l * 128);
+      sm100::prefetch_l2_line(row + rbyte0);
+    }
+  };
+  for (int a = 1; a <= kPrefetchAhead; ++a) prefetch(entry(a));
+  int t_next = entry(0), t_prefetch = entry(kPrefetchAhead + 1);
+  const int tile = lane >> 2, quad4 = lane & 3;
+  for (int j = 0; j < nb; ++j) {
+    const int st = j % kPairStages, use = j / kPairStages;
+    const int my_t = t_next, pf_t = t_prefetch;
+    t_next = entry(j + 1);
+    t_prefetch = entry(j + kPrefetchAhead + 2);
+    prefetch(pf_t);
+    if (use >= 1 && !sm100::mbar_wait_relaxed(&ctl.kv_empty[st], (use - 1) & 1, abort_flag, p.status, kWaitKvEmpty))
+      break;
+    const bool my_ok = my_t >= 0 && my_t < len;
+    if (lane < 16) ctl.valid[st][pw * 16 + lane] = my_ok ? 1 : 0;
+    const int my_row = row_base + (my_ok ? my_t : 0);   // an invalid entry fetches row 0: finite data under a zero weight
+    const int r0 = __shfl_sync(0xffffffffu, my_row, 4 * quad4 + 0), r1 = __shfl_sync(0xffffffffu, my_row, 4 * quad4 + 1);
+    const int r2 = __shfl_sync(0xffffffffu, my_row, 4 * quad4 + 2), r3 = __shfl_sync(0xffffffffu, my_row, 4 * quad4 + 3);
+    if (lane == 0) {
+      sm100::mbar_arrive_expect_tx(&ctl.kv_full[st][0], 2 * 16 * 128);
+      sm100::mbar_arrive_expect_tx(&ctl.kv_full[st][1], 2 * 16 * 128 + 16 * 64);
+    }
+    __syncwarp();
+    uint8_t* dst = kv_tile + st * kPairStageBytes;
+    const int first = pw * 16 + 4 * quad4;
+    if (tile < 4)
+      sm100::tma_gather4_2d(dst + tile * kChunkBytes + first * 128, map_v, &ctl.kv_full[st][tile >> 1],
+                            rank * 256 + tile * 64, r0, r1, r2, r3);
+    else if (tile == 4)
+      sm100::tma_gather4_2d(dst + kPairRopeOffset + first * 64, map_r, &ctl.kv_full[st][1], 512 + rank * 32, r0, r1, r2,
+                            r3);
+  }
+}
+
+template <bool kTmaGather>
 __global__ void __cluster_dims__(2, 1, 1) __maxnreg__(80)
-mla_sparse_decode_pair_kernel(const MlaParams p) {
+mla_sparse_decode_pair_kernel(const MlaParams p, const __grid_constant__ CUtensorMap map_v,
+                              const __grid_constant__ CUtensorMap map_r) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_rope = base;                              // this CTA's 32 rotary columns of Q, 128 heads x 64 bytes
@@ -609,7 +672,7 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
-      for (int c = 0; c < kPairTiles; ++c) sm100::mbar_init(&ctl.kv_full[s][c], 128);
+      for (int c = 0; c < kPairTiles; ++c) sm100::mbar_init(&ctl.kv_full[s][c], kTmaGather ? 4 : 128);
       sm100::mbar_init(&ctl.kv_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -791,7 +854,10 @@ mla_sparse_decode_pair_kernel(const MlaParams p) {
     // each warp owns 16 of every block's 64 rows and copies this CTA's slice of them (36 sixteen-byte
     // pieces per row)
     sm100::reg_dec<56>();
-    pair_produce(p, ctl, kv_tile, warp - 9, lane, b, j0, nb, len, (int)rank);
+    if (kTmaGather)
+      pair_produce_tma(p, ctl, kv_tile, warp - 9, lane, b, j0, nb, len, (int)rank, &map_v, &map_r);
+    else
+      pair_produce(p, ctl, kv_tile, warp - 9, lane, b, j0, nb, len, (int)rank);
   } else if (warp == 8) {
     // ---------------------------------------------------------------- Q.K^T issuer
     // Two issuing threads (this one and the P.V issuer in warp 17) instead of one that polls: each
@@ -1124,10 +1190,26 @@ extern "C" int mla_sparse_decode_multi_launcher(cab_bf16* out, const cab_bf16* q
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   if (status && cudaMemsetAsync(status, 0, sizeof(int), stream) != cudaSuccess) return CAB_ERR_LAUNCH;
-  // config 1 forces the single-CTA kernel (64 heads per CTA); otherwise 128-head groups run on CTA pairs
+  // config 1 forces the single-CTA kernel (64 heads per CTA); otherwise 128-head groups run on CTA pairs,
+  // gathering rows with TMA (config 2: with 16-byte cp.async copies instead)
   if (config != 1 && Hh % kPairHeads == 0) {
-    if (!cab::ensure_dynamic_smem<&mla_sparse_decode_pair_kernel>(kPairSmemBytes)) return CAB_ERR_LAUNCH;
-    mla_sparse_decode_pair_kernel<<<dim3(2 * (Hh / kPairHeads), nsplit, B), kPairThreads, kPairSmemBytes, stream>>>(p);
+    const dim3 grid(2 * (Hh / kPairHeads), nsplit, B);
+    CUtensorMap map_v, map_r;
+    const unsigned long long cache_rows = (unsigned long long)(B / Sq) * (unsigned long long)S;
+    const bool tma = config != 2 && cache_rows <= 0x7fffffffULL &&
+                     sm100::make_tmap_2d(&map_v, kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cache_rows, kDqk, 1, 64,
+                                         CU_TENSOR_MAP_SWIZZLE_128B) &&
+                     sm100::make_tmap_2d(&map_r, kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cache_rows, kDqk, 1, 32,
+                                         CU_TENSOR_MAP_SWIZZLE_64B);
+    if (tma) {
+      if (!cab::ensure_dynamic_smem<&mla_sparse_decode_pair_kernel<true>>(kPairSmemBytes)) return CAB_ERR_LAUNCH;
+      mla_sparse_decode_pair_kernel<true><<<grid, kPairThreads, kPairSmemBytes, stream>>>(p, map_v, map_r);
+    } else {
+      memset(&map_v, 0, sizeof(map_v));
+      memset(&map_r, 0, sizeof(map_r));
+      if (!cab::ensure_dynamic_smem<&mla_sparse_decode_pair_kernel<false>>(kPairSmemBytes)) return CAB_ERR_LAUNCH;
+      mla_sparse_decode_pair_kernel<false><<<grid, kPairThreads, kPairSmemBytes, stream>>>(p, map_v, map_r);
+    }
   } else {
     if (!cab::ensure_dynamic_smem<&mla_sparse_decode_kernel>(kSmemBytes)) return CAB_ERR_LAUNCH;
     mla_sparse_decode_kernel<<<dim3(Hh / kHeads, nsplit, B), kThreads, kSmemBytes, stream>>>(p);

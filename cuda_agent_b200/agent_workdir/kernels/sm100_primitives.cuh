@@ -203,6 +203,20 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Row gather: four rows r0..r3 of a 2-D tensor, box columns [c0, c0 + box width) of each, land as four
+// consecutive rows at smem_dst (the tensor map's box is 1 row high; its swizzle applies as for a tiled load,
+// so 4-row pieces written at their place inside a 1024-byte-aligned tile give the tile a tiled load would
+// give). Completion (4 x box bytes) counts on `bar`. No multicast.
+__device__ __forceinline__ void tma_gather4_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int r0,
+                                               int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(r0), "r"(r1),
+        "r"(r2), "r"(r3)
+      : "memory");
+}
+
 // 2-D tiled store smem -> global (bulk async group). The smem tile must have been made
 // visible to the async proxy (fence_proxy_async) by its writers first.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {

@@ -85,7 +85,9 @@ def main(argv=None) -> int:
     parser.add_argument("--torch-load", action="store_true",
                         help="single torch.utils.cpp_extension.load build, as the reference does")
     args = parser.parse_args(argv)
-    if args.torch_load:
+    # a workspace exported for one task stands alone (no package around it): the reference's route is the only one
+    standalone = not (WORKDIR.parent / "build.py").exists()
+    if args.torch_load or standalone:
         return compile_with_torch_load(Path.cwd())
     return compile_incremental()
 

@@ -37,8 +37,9 @@ def test_matches_oracle(cuda_device, B, Hh, S, topk, min_len, nsplit):
     idx[0, 0, 3] = -1
     idx[B - 1, 0, topk // 2] = S + 5
     ref = m.Model(B, Hh, S, topk)(q, kv, seq_len, idx)
-    # config 0: 128-head groups run on CTA pairs; config 1 forces the 64-heads-per-CTA kernel
-    for config in ((0, 1) if Hh % 128 == 0 else (0,)):
+    # config 0: 128-head groups run on CTA pairs that gather rows with TMA (tile::gather4); config 2: the same
+    # pairs gathering with cp.async; config 1 forces the 64-heads-per-CTA kernel
+    for config in ((0, 2, 1) if Hh % 128 == 0 else (0,)):
         out = run(cuda_device, q, kv, seq_len, idx, nsplit, config)
         assert torch.isfinite(out.float()).all()
         err = float((out.float() - ref.float()).abs().max())

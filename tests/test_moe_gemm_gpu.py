@@ -120,3 +120,23 @@ def test_bounded_wait_gives_up_and_the_kernel_returns(cuda_device):
     torch.cuda.synchronize()
     assert int(status) == 0
     test_dense_down_projection(cuda_device, 128, 256, 128)
+
+
+def test_one_process_drives_two_gpus(cuda_device):
+    """Kernel attributes (the opt-in to large dynamic shared memory) are kept per device: the same process runs
+    the tensor-core kernels on device 0 and then on device 1."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs on the box")
+    from test_mla_gpu import run as run_mla
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
+    gen = torch.Generator().manual_seed(3)
+    q, kv, seq_len, idx = m.make_inputs(2, 128, 300, 128, 100, gen)
+    ref = m.Model(2, 128, 300, 128)(q, kv, seq_len, idx)
+    for index in (0, 1):
+        dev = torch.device("cuda", index)
+        with torch.cuda.device(dev):
+            test_dense_down_projection(dev, 128, 256, 512)
+            test_dense_gate_up_swiglu_requant(dev, 128, 128, 128)
+            for config in (0, 1):
+                out = run_mla(dev, q, kv, seq_len, idx, 2, config)
+                assert float((out.float() - ref.float()).abs().max()) <= 2e-2
