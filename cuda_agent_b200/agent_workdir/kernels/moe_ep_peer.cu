@@ -111,7 +111,9 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 }
 
 // ------------------------------------------------------------------ plan
-// CTA d: which tokens have an expert on rank d, and the rank of each such token among them.
+// CTA d: which tokens have an expert on rank d, and the rank of each such token among them. A thread owns a
+// run of consecutive tokens (at most 32: t_cap <= 32768), remembers which of them go to rank d in a bit mask,
+// and after the block scan writes their positions without reading the routing table again.
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int* __restrict__ topk_idx, int T, int k, int e_local, int world, int t_cap,
                int* __restrict__ copy_pos, int* __restrict__ back_row, int* __restrict__ n_copies) {
@@ -119,15 +121,29 @@ ep_plan_kernel(const int* __restrict__ topk_idx, int T, int k, int e_local, int 
   const int d = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int per = (T + 1023) / 1024;
   const int t0 = tid * per, t1 = min(T, t0 + per);
-  int mine = 0;
-  for (int t = t0; t < t1; ++t) {
-    bool has = false;
-    for (int j = 0; j < k; ++j) {
-      const int e = __ldg(topk_idx + (size_t)t * k + j);
-      has |= (e >= 0 && e / e_local == d);
+  const int lo = d * e_local, hi = lo + e_local;
+  uint32_t mask = 0;
+  if ((k & 3) == 0) {
+    for (int t = t0; t < t1; ++t) {
+      const int4* row = reinterpret_cast<const int4*>(topk_idx + (size_t)t * k);
+      bool has = false;
+      for (int j = 0; j < (k >> 2); ++j) {
+        const int4 e = __ldg(row + j);
+        has |= (e.x >= lo && e.x < hi) | (e.y >= lo && e.y < hi) | (e.z >= lo && e.z < hi) | (e.w >= lo && e.w < hi);
+      }
+      mask |= (has ? 1u : 0u) << (t - t0);
     }
-    mine += has ? 1 : 0;
+  } else {
+    for (int t = t0; t < t1; ++t) {
+      bool has = false;
+      for (int j = 0; j < k; ++j) {
+        const int e = __ldg(topk_idx + (size_t)t * k + j);
+        has |= (e >= lo && e < hi);
+      }
+      mask |= (has ? 1u : 0u) << (t - t0);
+    }
   }
+  const int mine = __popc(mask);
   int inc = mine;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
@@ -140,11 +156,7 @@ ep_plan_kernel(const int* __restrict__ topk_idx, int T, int k, int e_local, int 
   for (int w = 0; w < warp; ++w) base += warp_tot[w];
   int pos = base + inc - mine;
   for (int t = t0; t < t1; ++t) {
-    bool has = false;
-    for (int j = 0; j < k; ++j) {
-      const int e = __ldg(topk_idx + (size_t)t * k + j);
-      has |= (e >= 0 && e / e_local == d);
-    }
+    const bool has = (mask >> (t - t0)) & 1u;
     copy_pos[(size_t)t * world + d] = has ? pos : -1;
     back_row[(size_t)t * world + d] = has ? d * t_cap + pos : -1;
     pos += has ? 1 : 0;
@@ -377,7 +389,7 @@ extern "C" int moe_ep_peer_create(void** ctx_out, int rank, int world, int t_cap
   if (world <= 0 || world > kMaxWorld || rank < 0 || rank >= world || t_cap <= 0 || H <= 0 || H % 256 != 0 || k <= 0 ||
       k > kMaxK || e_local <= 0 || e_local > 256)
     return CAB_ERR_BAD_ARGUMENT;
-  if ((long long)world * t_cap * k > (1LL << 30)) return CAB_ERR_TOO_LARGE;
+  if ((long long)world * t_cap * k > (1LL << 30) || t_cap > 32768) return CAB_ERR_TOO_LARGE;
   Ctx* c = new (std::nothrow) Ctx();
   if (!c) return CAB_ERR_LAUNCH;
   c->L = make_layout(world, t_cap, H, k);

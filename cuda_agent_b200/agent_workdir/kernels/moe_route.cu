@@ -17,6 +17,7 @@
 // The selection kernels run one warp per token with the token's E <= 256 scores
 // spread over the lanes (expert e lives in lane e % 32, slot e / 32).
 #include "cab_common.cuh"
+#include "sm100_primitives.cuh"
 
 namespace {
 
@@ -111,6 +112,122 @@ router_logits_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict
       __syncthreads();
     }
   }
+}
+
+// ------------------------------------------------------------------ logits on tcgen05
+// The same product for large batches: a CTA takes 128 tokens and all E experts (E a multiple of 32, at most
+// 256), TMA brings 128 x 64 bf16 of x and E x 64 of the router weight per stage (128-byte swizzle), one thread
+// issues tcgen05.mma kind::f16 (M 128, N E, K 16) into a single fp32 accumulator in tensor memory that runs over
+// the whole of H, and four warps write the rows out. One accumulation chain in k order per (token, expert), so
+// the result does not depend on scheduling.
+constexpr int kTcStages = 4;
+struct __align__(16) TcControl {
+  uint64_t full[kTcStages], empty[kTcStages], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(192, 1)
+router_logits_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                        float* __restrict__ logits, int T, int H, int E, uint32_t tmem_cols) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stage_bytes = 128 * 128 + E * 128;
+  TcControl& ctl = *reinterpret_cast<TcControl*>(tiles + kTcStages * stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * 128;
+  const int ksteps = H / 64;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) { sm100::mbar_init(&ctl.full[s], 1); sm100::mbar_init(&ctl.empty[s], 1); }
+    sm100::mbar_init(&ctl.acc_full, 1);
+    ctl.abort_flag = 0;
+    sm100::mbar_fence_init();
+    sm100::prefetch_tensormap(&tmap_x);
+    sm100::prefetch_tensormap(&tmap_w);
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(&ctl.tmem_base, tmem_cols);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  sm100::tc_fence_after_sync();
+  const uint32_t tmem_base = ctl.tmem_base;
+  volatile int* abort_flag = &ctl.abort_flag;
+
+  if (warp == 0 && lane == 0) {
+    int stage = 0; uint32_t phase = 0;
+    for (int ks = 0; ks < ksteps; ++ks) {
+      if (!sm100::mbar_wait(&ctl.empty[stage], phase ^ 1, abort_flag, nullptr, 0)) break;
+      uint8_t* dst = tiles + stage * stage_bytes;
+      sm100::mbar_arrive_expect_tx(&ctl.full[stage], stage_bytes);
+      sm100::tma_load_2d(dst, &tmap_x, &ctl.full[stage], ks * 64, m0);
+      sm100::tma_load_2d(dst + 128 * 128, &tmap_w, &ctl.full[stage], ks * 64, 0);
+      if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+    }
+  } else if (warp == 1 && lane == 0) {
+    const uint32_t idesc = sm100::umma_idesc(1 /* bf16 */, 128, E);
+    int stage = 0; uint32_t phase = 0;
+    bool ok = true;
+    for (int ks = 0; ks < ksteps; ++ks) {
+      if (!sm100::mbar_wait(&ctl.full[stage], phase, abort_flag, nullptr, 0)) { ok = false; break; }
+      sm100::tc_fence_after_sync();
+      const uint32_t a_addr = sm100::smem_u32(tiles + stage * stage_bytes);
+      const uint64_t a_desc = sm100::umma_desc_k_sw128(a_addr);
+      const uint64_t b_desc = sm100::umma_desc_k_sw128(a_addr + 128 * 128);
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4)   // 16 bf16 = 32 bytes of K per instruction: +2 in 16-byte units
+        sm100::umma_f16(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (ks > 0 || k4 > 0) ? 1u : 0u);
+      sm100::umma_commit(&ctl.empty[stage]);
+      if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+    }
+    if (ok) sm100::umma_commit(&ctl.acc_full);
+  } else if (warp >= 2) {
+    const int quad = warp & 3;                       // the TMEM lane quadrant a warp may read is warp id % 4
+    const int t = m0 + quad * 32 + lane;
+    if (sm100::mbar_wait(&ctl.acc_full, 0, abort_flag, nullptr, 0)) {
+      sm100::tc_fence_after_sync();
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+      for (int c = 0; c < E; c += 32) {
+        uint32_t v[32];
+        sm100::tmem_ld_32x32(lane_base + c, v);
+        sm100::tmem_ld_wait();
+        if (t < T) {
+          float4* dst = reinterpret_cast<float4*>(logits + (size_t)t * E + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
+                                 __uint_as_float(v[4 * i + 3]));
+        }
+      }
+    }
+  }
+  sm100::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tc_fence_after_sync();
+    sm100::tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// Launches the tensor-core form when the shapes fit it; returns false when the caller should use the other kernel.
+bool launch_router_logits_tc(float* logits, const cab_bf16* x, const cab_bf16* wr, int T, int H, int E,
+                             cudaStream_t stream, int& rc) {
+  if (T < 512 || E % 32 != 0 || E > 256 || H % 64 != 0 || !cab::aligned_to(logits, 16)) return false;
+  CUtensorMap tx, tw;
+  if (!sm100::make_tmap_2d_sw128(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)T, (uint64_t)H, 128, 64) ||
+      !sm100::make_tmap_2d_sw128(&tw, wr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)E, (uint64_t)H, (uint32_t)E, 64))
+    return false;
+  const int smem = kTcStages * (128 * 128 + E * 128) + (int)sizeof(TcControl) + 1024;
+  if (!cab::ensure_dynamic_smem<&router_logits_tc_kernel>(kTcStages * (128 * 128 + 256 * 128) + (int)sizeof(TcControl) + 1024)) {
+    rc = CAB_ERR_LAUNCH;
+    return true;
+  }
+  uint32_t cols = 32;
+  while ((int)cols < E) cols <<= 1;
+  router_logits_tc_kernel<<<(T + 127) / 128, 192, smem, stream>>>(tx, tw, logits, T, H, E, cols);
+  rc = cab::launch_status();
+  return true;
 }
 
 // ------------------------------------------------------------------ selection
@@ -251,12 +368,14 @@ bool route_args_ok(int T, int E, int k) { return T >= 0 && E > 0 && E <= kMaxE &
 
 extern "C" int moe_router_logits_launcher(float* logits, const cab_bf16* x, const cab_bf16* wr,
                                           int T, int H, int E, int config, cudaStream_t stream) {
-  (void)config;
   if (T == 0) return CAB_OK;
   if (!logits || !x || !wr) return CAB_ERR_BAD_ARGUMENT;
   if (T < 0 || H <= 0 || E <= 0 || H % 32 != 0 || E % 8 != 0) return CAB_ERR_BAD_ARGUMENT;
   if (!cab::aligned_to(x, 16) || !cab::aligned_to(wr, 16) || !cab::aligned_to(logits, 8))
     return CAB_ERR_MISALIGNED;
+  // config 1 keeps the mma.sync kernels for every shape; otherwise large batches go to the tcgen05 kernel
+  int rc = CAB_OK;
+  if (config != 1 && launch_router_logits_tc(logits, x, wr, T, H, E, stream, rc)) return rc;
   const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
   const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(wr);
   // Every CTA reads the whole router weight, so a large weight (E*H) wants many tokens per CTA: 64

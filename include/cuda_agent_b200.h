@@ -108,7 +108,10 @@ int gdn_decode_launcher(float* state, float* out, const cab_bf16* q, const cab_b
 /* ------------------------------------------------------------------------- */
 
 /* logits[T,E] (fp32) = x[T,H] (bf16) . wr[E,H]^T (bf16), fp32 accumulation.   */
-/* H % 32 == 0, E % 8 == 0; x and wr 16-byte aligned.                           */
+/* H % 32 == 0, E % 8 == 0; x and wr 16-byte aligned. Batches of 512 tokens or   */
+/* more with E % 32 == 0, E <= 256 and H % 64 == 0 run on tcgen05 (TMA-fed, one   */
+/* accumulation chain per element); config 1 keeps the mma.sync kernel for every   */
+/* shape. Both sum in fp32; they agree to summation-order noise.                   */
 int moe_router_logits_launcher(float* logits, const cab_bf16* x, const cab_bf16* wr, int T, int H,
                                int E, int config, cab_stream_t stream);
 
@@ -227,7 +230,8 @@ int moe_grouped_gemm_fp8_launcher(int mode, void* out, float* out_scales_t, cons
 /* moe_ep_peer_buffer_bytes(world, t_cap, H, k) bytes plus small tables, on the     */
 /* current device. t_cap bounds the tokens per rank and call; every capacity is     */
 /* fixed here, so a layer call allocates nothing and never synchronises with the    */
-/* host. H % 256 == 0, k <= 32, world <= 16, e_local = experts on each rank <= 256.  */
+/* host. H % 256 == 0, k <= 32, world <= 16, t_cap <= 32768, e_local = experts on     */
+/* each rank <= 256.                                                               */
 /* All ranks must make the same sequence of layer calls.                           */
 /* ------------------------------------------------------------------------- */
 size_t moe_ep_peer_buffer_bytes(int world, int t_cap, int H, int k);

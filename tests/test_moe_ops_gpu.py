@@ -16,17 +16,20 @@ def i32(*shape, dev):
     return torch.full(shape, -7, dtype=torch.int32, device=dev)
 
 
-@pytest.mark.parametrize("T,H,E", [(96, 256, 8), (33, 512, 64), (4096, 2048, 64), (70, 7168, 256), (16, 64, 72)])
+# batches of 512 tokens and more with E % 32 == 0 take the tcgen05 kernel (config 0), the rest and config 1 mma.sync
+@pytest.mark.parametrize("T,H,E", [(96, 256, 8), (33, 512, 64), (4096, 2048, 64), (70, 7168, 256), (16, 64, 72),
+                                   (1100, 7168, 256), (513, 128, 32), (640, 2048, 96)])
 def test_router_logits(cuda_device, T, H, E):
     from cuda_agent_b200 import capi
     gen = torch.Generator().manual_seed(T + E)
     x = torch.randn(T, H, generator=gen).to(torch.bfloat16)
     wr = (torch.randn(E, H, generator=gen) * 0.02).to(torch.bfloat16)
     ref = x.double() @ wr.double().t()
-    out = torch.full((T, E), float("nan"), device=cuda_device)
-    capi.moe_router_logits(out, x.to(cuda_device), wr.to(cuda_device))
-    err = (out.cpu().double() - ref).abs().max()
-    assert float(err) < 2e-5 * float(ref.abs().max()) + 1e-6, float(err)
+    for config in (0, 1):
+        out = torch.full((T, E), float("nan"), device=cuda_device)
+        capi.moe_router_logits(out, x.to(cuda_device), wr.to(cuda_device), config)
+        err = (out.cpu().double() - ref).abs().max()
+        assert float(err) < 2e-5 * float(ref.abs().max()) + 1e-6, (config, float(err))
 
 
 @pytest.mark.parametrize("T,E,k", [(1, 8, 2), (96, 8, 2), (4096, 64, 6), (1000, 256, 8), (50, 40, 5), (17, 64, 32)])
