@@ -3,7 +3,7 @@
 Nothing here computes an operator's result in torch on the timed GPU path: torch draws the synthetic
 inputs (and quantises the synthetic weights once, untimed); every timed GPU step is a call into the C ABI
 or into ``cuda_extension``. The ``cpu_*`` functions time the eager oracles on the host cores (the reported
-CPU baseline), and ``ep_parity`` is the checker leg of the expert-parallel line.
+CPU baseline), and ``MoeEpWorkload.parity`` is the checker leg of the expert-parallel line.
 """
 from __future__ import annotations
 
@@ -120,14 +120,11 @@ class Pipeline:
         self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self.in_ready = [torch.cuda.Event() for _ in range(2)]
         self.in_free = [torch.cuda.Event() for _ in range(2)]
-        self.out_done = [torch.cuda.Event() for _ in range(2)]
 
     def run(self, n):
         stream = torch.cuda.current_stream(self.dev)
         for e in self.in_free:
             e.record(stream)
-        for e in self.out_done:
-            e.record(self.copy_out)
 
         def up(i):
             s = i % 2
@@ -149,7 +146,6 @@ class Pipeline:
                 self.copy_out.wait_event(done)
                 self.download(out, s)
                 out.record_stream(self.copy_out)
-                self.out_done[s].record(self.copy_out)
         self.copy_out.synchronize()
         stream.synchronize()
 
