@@ -391,6 +391,7 @@ def moe_ep_record(ctx: Ctx, cpu_baseline: bool):
     args, torch = ctx.args, ctx.torch
     wl = bw.MoeEpWorkload(ctx.dev, ctx.rank, ctx.world, mode=args.ep_mode)
     steps, warmup = min(args.steps, 30), min(args.warmup, 5)
+    ctx.barrier()                     # every rank's weights and exchange buffers exist before the first call
     out = wl.step()
     torch.cuda.synchronize()
     parity = wl.parity(out) if ctx.rank == 0 else None
