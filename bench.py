@@ -308,6 +308,11 @@ def moe_record(ctx: Ctx, cpu_baseline: bool):
     assert wl.status.cpu().tolist() == [0, 0]
     tflops = wl.gemm_flops / (ms_gemm * 1e-3) / 1e12
     peak2 = 2.0 * ctx.peaks["bf16_tflops"]
+    try:
+        lib_burst, lib_sustained = bw.library_fp8_gemm_tflops(ctx.dev)
+    except Exception as exc:                      # a yardstick only: the line stands without it
+        lib_burst = lib_sustained = None
+        print(f"bench.py: library fp8 yardstick unavailable: {exc}", file=sys.stderr)
     kernel = "moe_gemm_fp8_kernel<0> + <1>"
     rec = {
         "metric": "moe_fp8_grouped_gemm_tflops", "value": round(tflops, 2), "unit": "TFLOP/s", "n_gpus": 1,
@@ -326,6 +331,9 @@ def moe_record(ctx: Ctx, cpu_baseline: bool):
                      "unit": "TFLOP/s", "frac": round(tflops / NOMINAL_FP8_TFLOPS, 4),
                      "peak_source": "nominal fp8 dense (no measured fp8 figure exists)",
                      "frac_of_2x_measured_bf16": round(tflops / peak2, 4), "peak_2x_measured_bf16": peak2,
+                     "library_dense_fp8_8192_cubed_tflops": None if lib_burst is None else
+                     {"burst": round(lib_burst, 1), "sustained": round(lib_sustained, 1),
+                      "frac_of_sustained": round(tflops / lib_sustained, 4)},
                      "traffic": NCU_TRAFFIC[kernel]},
     }
     if cpu_baseline:

@@ -330,6 +330,34 @@ class MlaWorkload:
                         lambda o, s: ho[s].copy_(o, non_blocking=True))
 
 
+# --------------------------------------------------------------------------------------------- yardstick
+def library_fp8_gemm_tflops(dev, n=8192, burst_iters=10, sustained_s=0.5):
+    """What the vendor library's dense e4m3 GEMM (torch._scaled_mm -> cuBLASLt, per-tensor scales, n^3) reaches on
+    this GPU right now: (best single call, average over `sustained_s` of back-to-back calls), TFLOP/s. A yardstick
+    for the roofline record only (no measured fp8 peak is provided); nothing of the product calls it."""
+    a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+    b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()          # column-major second operand
+    one = torch.ones((), device=dev)
+    run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    best = 0.0
+    for _ in range(burst_iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); run(); e1.record()
+        torch.cuda.synchronize()
+        best = max(best, 2.0 * n ** 3 / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    iters = max(10, int(sustained_s / (2.0 * n ** 3 / (best * 1e12))))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return best, 2.0 * n ** 3 * iters / (e0.elapsed_time(e1) * 1e-3) / 1e12
+
+
 # --------------------------------------------------------------------------------------------- timing helpers
 def time_cuda(fn, steps: int, warmup: int) -> float:
     """Milliseconds per call between two CUDA events on the current stream."""
