@@ -416,10 +416,14 @@ extern "C" int moe_ep_peer_create(void** ctx_out, int rank, int world, int t_cap
   c->status = reinterpret_cast<int*>(q);
   fill_ones_kernel<<<(unsigned)((tw + 255) / 256), 256>>>(c->ones, tw);
   if (cudaDeviceSynchronize() != cudaSuccess) { cudaFree(c->base); cudaFree(local); delete c; return CAB_ERR_LAUNCH; }
+  c->side_stream = nullptr; c->fork_event = nullptr; c->join_event = nullptr;
   if (cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->fork_event, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&c->join_event, cudaEventDisableTiming) != cudaSuccess) {
+    if (c->fork_event) cudaEventDestroy(c->fork_event);
+    if (c->side_stream) cudaStreamDestroy(c->side_stream);
     cudaFree(c->base); cudaFree(local); delete c;
+    cudaGetLastError();
     return CAB_ERR_LAUNCH;
   }
   c->peers.base[rank] = c->base;
@@ -478,6 +482,8 @@ extern "C" int moe_ep_peer_connect_local(void* ctx, void* const* all_ctx) {
 extern "C" int moe_ep_peer_destroy(void* ctx) {
   Ctx* c = as_ctx(ctx);
   if (!c) return CAB_OK;
+  int caller_device = -1;
+  cudaGetDevice(&caller_device);          // the caller's current device is put back before returning
   cudaSetDevice(c->device);
   cudaDeviceSynchronize();
   for (int r = 0; r < kMaxWorld; ++r)
@@ -488,6 +494,8 @@ extern "C" int moe_ep_peer_destroy(void* ctx) {
   cudaFree(c->copy_pos);     // first pointer of the local block
   cudaFree(c->base);
   delete c;
+  if (caller_device >= 0) cudaSetDevice(caller_device);
+  cudaGetLastError();
   return CAB_OK;
 }
 
