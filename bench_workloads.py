@@ -208,7 +208,7 @@ class MoeEpWorkload:
     SHARED_ID = 100000      # expert id under which the shared expert's weights are drawn
 
     def __init__(self, dev, rank, world, T=8192, H=7168, I=2048, E=256, k=8, seed=1238, mode="peer", group=None,
-                 gemm_ctas=0):
+                 gemm_ctas=0, connect=True):
         from cuda_agent_b200 import ep
         self.T, self.H, self.I, self.E, self.k, self.world, self.rank = T, H, I, E, k, world, rank
         self.dev, self.seed, self.mode = dev, seed, mode
@@ -227,7 +227,8 @@ class MoeEpWorkload:
         shared = expert_weights(dev, seed, self.SHARED_ID, H, I)
         self.ops = ep.CudaOps(self.router_w, self.router_bias, w13_q, w13_s, w2_q, w2_s, shared, k=k,
                               routing=1, n_group=8, topk_group=4, scaling=1.0, num_experts=E, gemm_ctas=gemm_ctas)
-        self.layer = ep.make_layer(self.ops, rank, world, T, mode=mode, group=group)
+        # connect=False: the caller joins several ranks of one process itself (PeerLayer.build_local)
+        self.layer = ep.make_layer(self.ops, rank, world, T, mode=mode, group=group) if connect else None
         self.flops_per_gpu = 6 * T * k * H * I + 6 * T * H * I          # routed + shared expert GEMMs
 
     def step(self, x=None):

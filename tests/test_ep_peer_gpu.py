@@ -24,7 +24,7 @@ def rel_l2(got, want):
     return float((got.float().cpu() - want.float()).norm() / want.float().norm())
 
 
-@pytest.mark.parametrize("cfg,world", [(0, 1), (0, 2), (1, 2), (1, 4)])
+@pytest.mark.parametrize("cfg,world", [(0, 1), (0, 2), (1, 2), (1, 4), (0, 8), (1, 8)])
 def test_virtual_ranks_on_one_gpu(cuda_device, cfg, world):
     from cuda_agent_b200.ep import PeerLayer
     m = load_oracle("moe", {"CAB_MOE_CONFIG": cfg})
@@ -95,6 +95,32 @@ def test_more_entries_than_capacity_are_dropped_and_flagged(cuda_device):
         for r in range(2):
             assert layers[r].status_codes() == [0] * 8
             assert rel_l2(outs[r], model(xs[r])) <= 2e-2
+    finally:
+        for l in layers:
+            l.close()
+
+
+def test_eight_ranks_at_full_dimensions_on_one_gpu(cuda_device):
+    """The expert-parallel layer as eight GPUs run it (H 7168, I 2048, 256 experts in blocks of 32, top-8 with
+    8 groups / top-4, shared expert), with the eight ranks stepped on one GPU and 256 tokens each: every rank's
+    first 48 tokens against the eager oracle."""
+    sys.path.insert(0, str(ROOT))
+    from bench_workloads import MoeEpWorkload
+    from cuda_agent_b200.ep import PeerLayer
+    world, T = 8, 256
+    wls = [MoeEpWorkload(cuda_device, r, world, T=T, connect=False) for r in range(world)]
+    layers = PeerLayer.build_local([w.ops for w in wls], T)
+    try:
+        for call in range(2):
+            outs = PeerLayer.forward_local(layers, [w.x for w in wls])
+            torch.cuda.synchronize()
+        for r in range(world):
+            assert layers[r].status_codes() == [0] * 8, (r, layers[r].status_codes())
+            p = wls[r].parity(outs[r], 48)
+            assert p["tokens_routed_differently"] <= 1 and p["rel_l2_identically_routed"] <= 2e-2, (r, p)
+        # one group of 32 experts per rank: a token travels to topk_group = 4 ranks at most
+        counts = torch.stack([l.debug_read(4, world, torch.int32).cpu() for l in layers])     # [dest, source]
+        assert world * T * 2 <= int(counts.sum()) <= world * T * 4
     finally:
         for l in layers:
             l.close()
