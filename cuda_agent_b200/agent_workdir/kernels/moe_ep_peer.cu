@@ -334,10 +334,13 @@ ep_return_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ 
     uint4* out = reinterpret_cast<uint4*>(peers.base[s] + L.off_back + ((size_t)rank * L.t_cap + p) * H * 2);
     for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      // no early exit per slot: the loads of four slots are in flight together (an empty slot adds 0 * 0)
+#pragma unroll 4
       for (int j = 0; j < k; ++j) {
-        if (rows[j] < 0) continue;
-        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[j] * H + col));
-        const float w = wts[j];
+        const bool live = rows[j] >= 0;
+        const uint4 raw = live ? __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[j] * H + col))
+                               : make_uint4(0u, 0u, 0u, 0u);
+        const float w = live ? wts[j] : 0.f;
         acc[0] = fmaf(w, cab::bf16_lo(raw.x), acc[0]); acc[1] = fmaf(w, cab::bf16_hi(raw.x), acc[1]);
         acc[2] = fmaf(w, cab::bf16_lo(raw.y), acc[2]); acc[3] = fmaf(w, cab::bf16_hi(raw.y), acc[3]);
         acc[4] = fmaf(w, cab::bf16_lo(raw.z), acc[4]); acc[5] = fmaf(w, cab::bf16_hi(raw.z), acc[5]);

@@ -197,11 +197,15 @@ moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int
   if (dst_row) my_dst = lane < k ? __ldg(dst_row + (size_t)t * k + lane) : -1;
   const int ndst = dst_row ? k : 1;
   const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+  // the next 256 columns are fetched before the current ones are quantised and stored
+  uint4 ahead = make_uint4(0, 0, 0, 0);
+  if (lane * 8 < H) ahead = __ldg(xrow + lane);
   for (int c0 = 0; c0 < H; c0 += 256) {
     const int col = c0 + lane * 8;
     const bool live = col < H;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live) raw = __ldg(xrow + (col >> 3));
+    const uint4 raw = ahead;
+    ahead = make_uint4(0, 0, 0, 0);
+    if (col + 256 < H) ahead = __ldg(xrow + ((col + 256) >> 3));
     float v[8] = {cab::bf16_lo(raw.x), cab::bf16_hi(raw.x), cab::bf16_lo(raw.y), cab::bf16_hi(raw.y),
                   cab::bf16_lo(raw.z), cab::bf16_hi(raw.z), cab::bf16_lo(raw.w), cab::bf16_hi(raw.w)};
     float amax = 0.f;
@@ -243,10 +247,14 @@ moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
   __syncthreads();
   for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    // an empty slot (a copy whose experts use fewer than k slots on this rank) adds 0 * 0: no early exit per
+    // slot, so that the loads of four slots are in flight together
+#pragma unroll 4
     for (int s = 0; s < k; ++s) {
-      if (rows[s] < 0) continue;          // an empty slot (a copy whose experts use fewer than k slots on this rank)
-      const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[s] * H + col));
-      const float ws = wts[s];
+      const bool live = rows[s] >= 0;
+      const uint4 raw = live ? __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[s] * H + col))
+                             : make_uint4(0u, 0u, 0u, 0u);
+      const float ws = live ? wts[s] : 0.f;
       acc[0] = fmaf(ws, cab::bf16_lo(raw.x), acc[0]); acc[1] = fmaf(ws, cab::bf16_hi(raw.x), acc[1]);
       acc[2] = fmaf(ws, cab::bf16_lo(raw.y), acc[2]); acc[3] = fmaf(ws, cab::bf16_hi(raw.y), acc[3]);
       acc[4] = fmaf(ws, cab::bf16_lo(raw.z), acc[4]); acc[5] = fmaf(ws, cab::bf16_hi(raw.z), acc[5]);
