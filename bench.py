@@ -465,10 +465,14 @@ def run_b200(args):
     line.setdefault("warmup", max(3, args.warmup))
     if args.workload == "all":
         sec = {}
-        if ctx.world == 1:
-            sec["moe"] = moe_record(ctx, cpu)
-        sec["mla"] = mla_record(ctx, cpu)
-        sec["moe_ep"] = moe_ep_record(ctx, cpu)
+        names = (["moe"] if ctx.world == 1 else []) + ["mla", "moe_ep"]
+        for name in names:
+            # a path that fails (on every rank alike) is reported under its name; the other paths keep their records
+            try:
+                sec[name] = RECORDS[name](ctx, cpu)
+            except Exception as exc:  # noqa: BLE001
+                sec[name] = {"error": f"{type(exc).__name__}: {exc}"[:400], "gpu_launches": 0}
+                ctx.torch.cuda.synchronize()
         line["secondary"] = sec
         line["gpu_launches"] += sum(r["gpu_launches"] for r in sec.values())
     line["clocks"] = ctx.finish()
