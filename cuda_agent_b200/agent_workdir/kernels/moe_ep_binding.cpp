@@ -12,6 +12,8 @@
 //   moe_ep_status(h) -> [8 ints]        blocking; zeros when nothing gave up (after at least one forward)
 //   moe_ep_destroy(h)
 //
+// entry_cap = (token, expert) entries this rank accepts per call (0: all of them on one rank, 1.5 x the
+// balanced share t_cap * k otherwise); what does not fit is dropped and flagged in status word 4.
 // w13_* / w2_* are THIS rank's experts ([e_local, ...]); the router and the shared expert are the same
 // on every rank. The wrapper follows the reference binding's pattern (agent_workdir/kernels/
 // axpby_binding.cpp:17-44): validate, allocate with torch::empty (the output, and once per handle the
@@ -35,7 +37,7 @@ struct Handle {
   torch::Tensor workspace;
   cab_moe_ep_layer_args args{};
   bool ran = false;
-  int H = 0, k = 0, e_local = 0, world = 0;
+  int H = 0, k = 0, e_local = 0, world = 0, t_cap = 0;
 };
 std::mutex g_mu;
 std::map<int64_t, Handle> g_handles;
@@ -52,7 +54,7 @@ int64_t moe_ep_create(int64_t rank, int64_t world, int64_t t_cap, int64_t H, int
   Handle hd;
   check_status(moe_ep_peer_create(&hd.ctx, (int)rank, (int)world, (int)t_cap, (int)H, (int)k, (int)e_local),
                "moe_ep_peer_create");
-  hd.H = (int)H; hd.k = (int)k; hd.e_local = (int)e_local; hd.world = (int)world;
+  hd.H = (int)H; hd.k = (int)k; hd.e_local = (int)e_local; hd.world = (int)world; hd.t_cap = (int)t_cap;
   const int64_t id = g_next++;
   g_handles[id] = hd;
   return id;
@@ -127,6 +129,10 @@ torch::Tensor moe_ep_forward(int64_t h, torch::Tensor x, torch::Tensor router_w,
     a.shared_w2_q = ptr<const cab_e4m3>(*shared_w2_q); a.shared_w2_s = ptr<const float>(*shared_w2_s);
   }
   a.E = (int)E; a.I = (int)I; a.routing = (int)routing; a.n_group = (int)n_group; a.topk_group = (int)topk_group;
+  // entry_cap 0: every entry when alone, 1.5 x the balanced share of t_cap * k entries otherwise
+  const int64_t balanced = (int64_t)hd.t_cap * hd.k;
+  if (entry_cap <= 0) entry_cap = hd.world == 1 ? balanced : balanced * 3 / 2;
+  TORCH_CHECK(entry_cap <= (int64_t)hd.world * balanced, "entry_cap exceeds world * t_cap * k");
   a.scaling = (float)scaling; a.entry_cap = (int)entry_cap; a.gemm_ctas = 0;
   const size_t need = moe_ep_peer_workspace_bytes(hd.ctx, &a);
   TORCH_CHECK(need > 0, "moe_ep_forward: the layer's shapes or routing arguments were rejected");
