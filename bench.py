@@ -80,6 +80,10 @@ def parse_args():
                          "or exchanged with NCCL all-to-all calls (nccl)")
     ap.add_argument("--nsplit", type=int, default=0, help="mla: splits of the selected rows (0 = the op's choice)")
     ap.add_argument("--min-region-s", type=float, default=MIN_REGION_S)
+    ap.add_argument("--ep-tokens", type=int, default=8192,
+                    help="moe_ep: tokens per GPU (the benchmark's figure is 8192; smaller values are for profiler captures)")
+    ap.add_argument("--ep-experts", type=int, default=256,
+                    help="moe_ep: routed experts over all ranks, a multiple of 8 groups (benchmark: 256)")
     return ap.parse_args()
 
 
@@ -397,12 +401,12 @@ def moe_ep_record(ctx: Ctx, cpu_baseline: bool):
     the output (pipelined)."""
     import bench_workloads as bw
     args, torch = ctx.args, ctx.torch
-    wl = bw.MoeEpWorkload(ctx.dev, ctx.rank, ctx.world, mode=args.ep_mode)
+    wl = bw.MoeEpWorkload(ctx.dev, ctx.rank, ctx.world, T=args.ep_tokens, E=args.ep_experts, mode=args.ep_mode)
     steps, warmup = min(args.steps, 30), min(args.warmup, 5)
     ctx.barrier()                     # every rank's weights and exchange buffers exist before the first call
     out = wl.step()
     torch.cuda.synchronize()
-    parity = wl.parity(out) if ctx.rank == 0 else None
+    parity = wl.parity(out, min(256, wl.T)) if ctx.rank == 0 else None
     del out
     ctx.barrier()
     ms, n = ctx.timed(lambda i: wl.step(), steps, warmup)

@@ -22,6 +22,15 @@ __host__ __device__ inline bool aligned_to(const void* p, size_t bytes) {
 // without synchronising the stream.
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? CAB_OK : CAB_ERR_LAUNCH; }
 
+// Threads for a CTA that walks `chunks` equal pieces of a row, one piece per thread and pass: the largest
+// multiple of 32 up to 256 that leaves no thread idle in the last pass (7168 bf16 columns in 16-byte pieces:
+// 896 = 4 x 224), else 256.
+inline int row_walk_threads(int chunks) {
+  for (int t = 256; t >= 128; t -= 32)
+    if (chunks % t == 0) return t;
+  return 256;
+}
+
 // Opt-in to more than 48 KB of dynamic shared memory for `Kernel`. The attribute belongs to the
 // (function, device) pair, so it is set once per device with that device current; one process may
 // drive several GPUs and several host threads.

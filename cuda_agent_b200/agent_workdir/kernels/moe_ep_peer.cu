@@ -14,15 +14,15 @@
 //
 // One layer call on a rank (all launches asynchronous on the caller's stream):
 //   plan      per destination rank, a scan over the tokens gives every (token, destination) copy its row
-//   dispatch  a warp per token quantises the row once (1x128 e4m3) and stores it, its scales and its
-//             (weight, local expert) slots straight into the destination ranks' recv_* rows; the CTA that
-//             finishes last publishes recv_flag on every peer (release at system scope)
+//   dispatch  warps quantise a token's row once (1x128 e4m3) and store it, its scales and its
+//             (weight, local expert) slots straight into the destination ranks' recv_* rows; a one-warp
+//             kernel behind it publishes recv_flag on every peer (release at system scope)
 //   receive   one small CTA waits (bounded) for the R flags, then the valid slots become sort keys
 //   permute   moe_permute_launcher sorts the keys by local expert into the padded row space
 //   gather    received rows are copied into that row space, scales transposed
 //   GEMMs     gate/up + SwiGLU + re-quantise, down
 //   return    per received copy, sum_j w_j y_j in fp32 -> bf16, stored into the source rank's back_rows;
-//             the last CTA publishes back_flag on every peer
+//             a one-warp kernel behind it publishes back_flag on every peer
 //   combine   one small CTA waits (bounded) for the R back flags; out[t] = sum over destinations of the
 //             partial rows (+ shared expert)
 //
@@ -38,6 +38,7 @@
 
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <cstring>
 #include <new>
 
@@ -87,7 +88,6 @@ struct Ctx {
   int* src_count;                // [world] copies received per source in the current call
   int* keys;                     // [world * t_cap * k]
   float* ones;                   // [t_cap * world]
-  unsigned* done;                // [2] last-CTA counters (dispatch, return)
   int* status;                   // [4] 0: wait for dispatch flags, 1: wait for return flags, 2, 3: spare
   cudaStream_t side_stream;      // the shared expert runs here, beside the exchange
   cudaEvent_t fork_event, join_event;
@@ -165,49 +165,65 @@ ep_plan_kernel(const int* __restrict__ topk_idx, int T, int k, int e_local, int 
 }
 
 // ------------------------------------------------------------------ dispatch
-// One warp per token: 1x128 e4m3 quantisation (the rule of moe_quant_dispatch_kernel) and stores into
-// every destination rank's receive rows. The CTA that finishes last publishes the flags.
+// One warp per token and 1024 columns: 1x128 e4m3 quantisation (the rule of moe_quant_dispatch_kernel) and stores into
+// every destination rank's receive rows. ep_publish_kernel, launched behind it, publishes the flags.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx,
                    const float* __restrict__ topk_w, const int* __restrict__ copy_pos,
-                   const int* __restrict__ n_copies, int T, int rank, int e_local, Layout L, PeerTable peers,
-                   unsigned* __restrict__ done, unsigned epoch) {
+                   int T, int rank, int e_local,
+                   const __grid_constant__ Layout L, const __grid_constant__ PeerTable peers) {
+  // a warp per (token, 1024-column segment); the warp of segment 0 also writes the token's side band
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int H = L.H, k = L.k, world = L.world;
-  if (t < T) {
+  const int segs = (H + 1023) >> 10;
+  // (the CTAs walk the segments with a grid stride: every CTA ends with a system-scope fence and a count,
+  // so there are a few per SM, not one per eight segments)
+  const long long n_items = (long long)T * segs, stride = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wi < n_items; wi += stride) {
+    const int t = (int)(wi / segs);
+    const int c0 = (int)(wi - (long long)t * segs) << 10;
     const int my_e = lane < k ? __ldg(topk_idx + (size_t)t * k + lane) : -1;
     const float my_w = lane < k ? __ldg(topk_w + (size_t)t * k + lane) : 0.f;
     const int my_dest = my_e >= 0 ? my_e / e_local : -1;
     const int my_pos = lane < world ? __ldg(copy_pos + (size_t)t * world + lane) : -1;   // lane d: copy for rank d
     const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)t * H);
-    for (int c0 = 0; c0 < H; c0 += 256) {
-      const int col = c0 + lane * 8;
-      const bool live = col < H;
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (live) raw = __ldg(xrow + (col >> 3));
-      float v[8] = {cab::bf16_lo(raw.x), cab::bf16_hi(raw.x), cab::bf16_lo(raw.y), cab::bf16_hi(raw.y),
-                    cab::bf16_lo(raw.z), cab::bf16_hi(raw.z), cab::bf16_lo(raw.w), cab::bf16_hi(raw.w)};
-      float amax = 0.f;
+    // the four 16-byte loads of a lane are issued before the first is used
+    {
+      uint4 raw4[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      for (int u = 0; u < 4; ++u) {
+        const int col = c0 + u * 256 + lane * 8;
+        raw4[u] = col < H ? __ldg(xrow + (col >> 3)) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-      for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-      const float scale = __fdiv_rn(fmaxf(amax, kAmaxFloor), kFp8Max);
+      for (int u = 0; u < 4; ++u) {
+        const int col = c0 + u * 256 + lane * 8;
+        const bool live = col < H;
+        if (c0 + u * 256 >= H) break;                    // warp-uniform: nothing left of the row
+        const uint4 raw = raw4[u];
+        float v[8] = {cab::bf16_lo(raw.x), cab::bf16_hi(raw.x), cab::bf16_lo(raw.y), cab::bf16_hi(raw.y),
+                      cab::bf16_lo(raw.z), cab::bf16_hi(raw.z), cab::bf16_lo(raw.w), cab::bf16_hi(raw.w)};
+        float amax = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = __fdiv_rn(v[j], scale);
-      const uint2 q = make_uint2(pack4_e4m3(v[0], v[1], v[2], v[3]), pack4_e4m3(v[4], v[5], v[6], v[7]));
-      for (int d = 0; d < world; ++d) {
-        const int pos = __shfl_sync(0xffffffffu, my_pos, d);
-        if (pos < 0 || !live) continue;
-        const size_t slot = (size_t)rank * L.t_cap + pos;
-        *reinterpret_cast<uint2*>(peers.base[d] + L.off_rows + slot * H + col) = q;
-        if ((lane & 15) == 0)
-          reinterpret_cast<float*>(peers.base[d] + L.off_side)[slot * L.side_ld + (col >> 7)] = scale;
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        const float scale = __fdiv_rn(fmaxf(amax, kAmaxFloor), kFp8Max);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fdiv_rn(v[j], scale);
+        const uint2 q = make_uint2(pack4_e4m3(v[0], v[1], v[2], v[3]), pack4_e4m3(v[4], v[5], v[6], v[7]));
+        for (int d = 0; d < world; ++d) {
+          const int pos = __shfl_sync(0xffffffffu, my_pos, d);
+          if (pos < 0 || !live) continue;
+          const size_t slot = (size_t)rank * L.t_cap + pos;
+          *reinterpret_cast<uint2*>(peers.base[d] + L.off_rows + slot * H + col) = q;
+          if ((lane & 15) == 0)
+            reinterpret_cast<float*>(peers.base[d] + L.off_side)[slot * L.side_ld + (col >> 7)] = scale;
+        }
       }
     }
     // slots of the side band: lane j < k holds entry j of the token
-    for (int d = 0; d < world; ++d) {
+    for (int d = 0; d < world && c0 == 0; ++d) {
       const int pos = __shfl_sync(0xffffffffu, my_pos, d);
       if (pos < 0 || lane >= k) continue;
       const size_t slot = (size_t)rank * L.t_cap + pos;
@@ -217,19 +233,20 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ 
       side[k + lane] = (uint32_t)(here ? my_e - d * e_local : -1);
     }
   }
-  // completion: every CTA's stores are fenced before its count; the last CTA fences again and publishes
-  __threadfence_system();
-  __syncthreads();
-  __shared__ bool is_last;
-  if (threadIdx.x == 0) is_last = (atomicAdd(done, 1u) == gridDim.x - 1u);
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence_system();
-  if (threadIdx.x < world) {
-    unsigned long long* flag = reinterpret_cast<unsigned long long*>(peers.base[threadIdx.x] + L.off_flag) + rank;
-    st_release_sys_u64(flag, ((unsigned long long)epoch << 32) | (unsigned)__ldg(n_copies + threadIdx.x));
-  }
-  if (threadIdx.x == 0) *done = 0;
+}
+
+// ------------------------------------------------------------------ publish
+// Runs after the kernel whose stores it announces (stream order: that kernel has completed, its stores to
+// this GPU and to the peers have been performed). Thread d writes this rank's flag on rank d, release at
+// system scope: (call number << 32) | counts[d], or the call number alone when counts is null.
+__global__ void __launch_bounds__(32)
+ep_publish_kernel(const __grid_constant__ PeerTable peers, size_t flag_offset, int rank, int world, unsigned epoch,
+                  const int* __restrict__ counts) {
+  const int d = threadIdx.x;
+  if (d >= world) return;
+  unsigned long long* flag = reinterpret_cast<unsigned long long*>(peers.base[d] + flag_offset) + rank;
+  const unsigned low = counts ? (unsigned)__ldg(counts + d) : 0u;
+  st_release_sys_u64(flag, ((unsigned long long)epoch << 32) | low);
 }
 
 // ------------------------------------------------------------------ bounded wait for R flags
@@ -312,14 +329,13 @@ ep_gather_kernel(uint8_t* __restrict__ a_q, float* __restrict__ a_s_t, const uin
 
 // ------------------------------------------------------------------ return
 // Per received copy: sum over its slots (ascending) of w_j * y[row_j], fp32 -> bf16, stored into the
-// source rank's back_rows; the last CTA publishes the flags.
+// source rank's back_rows; ep_publish_kernel, launched behind it, publishes the flags.
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ side,
-                 const int* __restrict__ src_count, const int* __restrict__ dst_row, int rank, Layout L,
-                 PeerTable peers, unsigned* __restrict__ done, unsigned epoch) {
+                 const int* __restrict__ src_count, const int* __restrict__ dst_row, int rank,
+                 const __grid_constant__ Layout L, const __grid_constant__ PeerTable peers) {
   __shared__ int rows[kMaxK];
   __shared__ float wts[kMaxK];
-  __shared__ bool is_last;
   const int k = L.k, H = L.H, world = L.world;
   for (int c = blockIdx.x;; c += gridDim.x) {
     int s, p;
@@ -334,17 +350,25 @@ ep_return_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ 
     uint4* out = reinterpret_cast<uint4*>(peers.base[s] + L.off_back + ((size_t)rank * L.t_cap + p) * H * 2);
     for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      // no early exit per slot: the loads of four slots are in flight together (an empty slot adds 0 * 0)
-#pragma unroll 4
-      for (int j = 0; j < k; ++j) {
-        const bool live = rows[j] >= 0;
-        const uint4 raw = live ? __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[j] * H + col))
-                               : make_uint4(0u, 0u, 0u, 0u);
-        const float w = live ? wts[j] : 0.f;
-        acc[0] = fmaf(w, cab::bf16_lo(raw.x), acc[0]); acc[1] = fmaf(w, cab::bf16_hi(raw.x), acc[1]);
-        acc[2] = fmaf(w, cab::bf16_lo(raw.y), acc[2]); acc[3] = fmaf(w, cab::bf16_hi(raw.y), acc[3]);
-        acc[4] = fmaf(w, cab::bf16_lo(raw.z), acc[4]); acc[5] = fmaf(w, cab::bf16_hi(raw.z), acc[5]);
-        acc[6] = fmaf(w, cab::bf16_lo(raw.w), acc[6]); acc[7] = fmaf(w, cab::bf16_hi(raw.w), acc[7]);
+      // slots in batches of eight: the batch's row loads are issued together, then added in ascending
+      // slot order (an empty slot contributes 0 * 0)
+      for (int j0 = 0; j0 < k; j0 += 8) {
+        uint4 raw[8];
+        float w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int j = j0 + u;
+          const bool live = j < k && rows[j] >= 0;
+          raw[u] = live ? __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[j] * H + col)) : make_uint4(0u, 0u, 0u, 0u);
+          w[u] = live ? wts[j] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc[0] = fmaf(w[u], cab::bf16_lo(raw[u].x), acc[0]); acc[1] = fmaf(w[u], cab::bf16_hi(raw[u].x), acc[1]);
+          acc[2] = fmaf(w[u], cab::bf16_lo(raw[u].y), acc[2]); acc[3] = fmaf(w[u], cab::bf16_hi(raw[u].y), acc[3]);
+          acc[4] = fmaf(w[u], cab::bf16_lo(raw[u].z), acc[4]); acc[5] = fmaf(w[u], cab::bf16_hi(raw[u].z), acc[5]);
+          acc[6] = fmaf(w[u], cab::bf16_lo(raw[u].w), acc[6]); acc[7] = fmaf(w[u], cab::bf16_hi(raw[u].w), acc[7]);
+        }
       }
       __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]), p1 = __floats2bfloat162_rn(acc[2], acc[3]);
       __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]), p3 = __floats2bfloat162_rn(acc[6], acc[7]);
@@ -354,17 +378,6 @@ ep_return_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ 
       out[col >> 3] = o;
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) is_last = (atomicAdd(done, 1u) == gridDim.x - 1u);
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence_system();
-  if (threadIdx.x < world) {
-    unsigned long long* flag = reinterpret_cast<unsigned long long*>(peers.base[threadIdx.x] + L.off_back_flag) + rank;
-    st_release_sys_u64(flag, (unsigned long long)epoch << 32);
-  }
-  if (threadIdx.x == 0) *done = 0;
 }
 
 __global__ void fill_ones_kernel(float* p, size_t n) {
@@ -415,7 +428,7 @@ extern "C" int moe_ep_peer_create(void** ctx_out, int rank, int world, int t_cap
   c->src_count = reinterpret_cast<int*>(q); q += (size_t)world * 4;
   c->keys = reinterpret_cast<int*>(q); q += tw * k * 4;
   c->ones = reinterpret_cast<float*>(q); q += tw * 4;
-  c->done = reinterpret_cast<unsigned*>(q); q += 16;
+  q += 16;
   c->status = reinterpret_cast<int*>(q);
   fill_ones_kernel<<<(unsigned)((tw + 255) / 256), 256>>>(c->ones, tw);
   if (cudaDeviceSynchronize() != cudaSuccess) { cudaFree(c->base); cudaFree(local); delete c; return CAB_ERR_LAUNCH; }
@@ -533,10 +546,11 @@ extern "C" int moe_ep_peer_dispatch_launcher(void* ctx, const cab_bf16* x, const
   c->epoch += 1;                       // this call's number; every rank makes the same sequence of calls
   ep_plan_kernel<<<L.world, 1024, 0, stream>>>(topk_idx, T, L.k, c->e_local, L.world, L.t_cap, c->copy_pos,
                                                c->back_row, c->n_copies);
-  const int grid = T > 0 ? (T + 7) / 8 : 1;
+  const long long warps = (long long)T * ((L.H + 1023) >> 10);
+  const unsigned grid = warps > 0 ? (unsigned)((warps + 7) / 8) : 1u;
   ep_dispatch_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, topk_w,
-                                               c->copy_pos, c->n_copies, T, c->rank, c->e_local, L, c->peers,
-                                               c->done, c->epoch);
+                                               c->copy_pos, T, c->rank, c->e_local, L, c->peers);
+  ep_publish_kernel<<<1, 32, 0, stream>>>(c->peers, L.off_flag, c->rank, L.world, c->epoch, c->n_copies);
   return cab::launch_status();
 }
 
@@ -562,7 +576,7 @@ extern "C" int moe_ep_peer_gather_launcher(void* ctx, cab_e4m3* a_q, float* a_sc
     return CAB_ERR_BAD_ARGUMENT;
   if (!cab::aligned_to(a_q, 16)) return CAB_ERR_MISALIGNED;
   const Layout& L = c->L;
-  ep_gather_kernel<<<cab::kNumSMs * 4, 256, 0, stream>>>(a_q, a_scales_t, c->base + L.off_rows,
+  ep_gather_kernel<<<cab::kNumSMs * 4, cab::row_walk_threads(L.H / 16), 0, stream>>>(a_q, a_scales_t, c->base + L.off_rows,
                                                          reinterpret_cast<const float*>(c->base + L.off_side),
                                                          c->src_count, dst_row, L.world, L.t_cap, L.k, L.H, L.side_ld,
                                                          ld_rows);
@@ -576,9 +590,10 @@ extern "C" int moe_ep_peer_return_launcher(void* ctx, const cab_bf16* y, const i
   if (!cab::aligned_to(y, 16)) return CAB_ERR_MISALIGNED;
   const Layout& L = c->L;
   const int grid = config > 0 ? config : cab::kNumSMs * 4;
-  ep_return_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(y),
+  ep_return_kernel<<<grid, cab::row_walk_threads(L.H / 8), 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(y),
                                              reinterpret_cast<const float*>(c->base + L.off_side), c->src_count,
-                                             dst_row, c->rank, L, c->peers, c->done + 1, c->epoch);
+                                             dst_row, c->rank, L, c->peers);
+  ep_publish_kernel<<<1, 32, 0, stream>>>(c->peers, L.off_back_flag, c->rank, L.world, c->epoch, nullptr);
   return cab::launch_status();
 }
 

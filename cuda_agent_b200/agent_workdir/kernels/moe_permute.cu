@@ -190,40 +190,50 @@ __global__ void __launch_bounds__(256)
 moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int k,
                           const int* __restrict__ dst_row, uint8_t* __restrict__ a_q,
                           float* __restrict__ sc_t, int ld_rows) {
+  // a warp per (token, 1024-column segment): long rows are shared by several warps
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
+  const int segs = (H + 1023) >> 10;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)T * segs) return;
+  const int t = (int)(w / segs);
+  const int c0 = (int)(w - (long long)t * segs) << 10;
   int my_dst = t;
   if (dst_row) my_dst = lane < k ? __ldg(dst_row + (size_t)t * k + lane) : -1;
   const int ndst = dst_row ? k : 1;
   const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)t * H);
-  // the next 256 columns are fetched before the current ones are quantised and stored
-  uint4 ahead = make_uint4(0, 0, 0, 0);
-  if (lane * 8 < H) ahead = __ldg(xrow + lane);
-  for (int c0 = 0; c0 < H; c0 += 256) {
-    const int col = c0 + lane * 8;
-    const bool live = col < H;
-    const uint4 raw = ahead;
-    ahead = make_uint4(0, 0, 0, 0);
-    if (col + 256 < H) ahead = __ldg(xrow + ((col + 256) >> 3));
-    float v[8] = {cab::bf16_lo(raw.x), cab::bf16_hi(raw.x), cab::bf16_lo(raw.y), cab::bf16_hi(raw.y),
-                  cab::bf16_lo(raw.z), cab::bf16_hi(raw.z), cab::bf16_lo(raw.w), cab::bf16_hi(raw.w)};
-    float amax = 0.f;
+  // the four 16-byte loads of a lane are issued before the first is used
+  {
+    uint4 raw4[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    for (int u = 0; u < 4; ++u) {
+      const int col = c0 + u * 256 + lane * 8;
+      raw4[u] = col < H ? __ldg(xrow + (col >> 3)) : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-    for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    const float scale = __fdiv_rn(fmaxf(amax, kAmaxFloor), kFp8Max);
+    for (int u = 0; u < 4; ++u) {
+      const int col = c0 + u * 256 + lane * 8;
+      const bool live = col < H;
+      if (c0 + u * 256 >= H) break;                      // warp-uniform: nothing left of the row
+      const uint4 raw = raw4[u];
+      float v[8] = {cab::bf16_lo(raw.x), cab::bf16_hi(raw.x), cab::bf16_lo(raw.y), cab::bf16_hi(raw.y),
+                    cab::bf16_lo(raw.z), cab::bf16_hi(raw.z), cab::bf16_lo(raw.w), cab::bf16_hi(raw.w)};
+      float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __fdiv_rn(v[j], scale);
-    const uint2 q = make_uint2(pack4_e4m3(v[0], v[1], v[2], v[3]), pack4_e4m3(v[4], v[5], v[6], v[7]));
-    for (int s = 0; s < ndst; ++s) {
-      const int row = dst_row ? __shfl_sync(0xffffffffu, my_dst, s) : t;
-      if (live && row >= 0) {
-        *reinterpret_cast<uint2*>(a_q + (size_t)row * H + col) = q;
-        if ((lane & 15) == 0) {
-          if (ROW_MAJOR_SCALES) sc_t[(size_t)row * (H >> 7) + (col >> 7)] = scale;
-          else sc_t[(size_t)(col >> 7) * ld_rows + row] = scale;
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+      const float scale = __fdiv_rn(fmaxf(amax, kAmaxFloor), kFp8Max);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __fdiv_rn(v[j], scale);
+      const uint2 q = make_uint2(pack4_e4m3(v[0], v[1], v[2], v[3]), pack4_e4m3(v[4], v[5], v[6], v[7]));
+      for (int s = 0; s < ndst; ++s) {
+        const int row = dst_row ? __shfl_sync(0xffffffffu, my_dst, s) : t;
+        if (live && row >= 0) {
+          *reinterpret_cast<uint2*>(a_q + (size_t)row * H + col) = q;
+          if ((lane & 15) == 0) {
+            if (ROW_MAJOR_SCALES) sc_t[(size_t)row * (H >> 7) + (col >> 7)] = scale;
+            else sc_t[(size_t)(col >> 7) * ld_rows + row] = scale;
+          }
         }
       }
     }
@@ -233,6 +243,7 @@ moe_quant_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int
 // ------------------------------------------------------------------ combine
 // out[t] = sum over slots (ascending) of w[t,slot] * y[dst_row[t*k+slot]] (+ extra[t]),
 // fp32 accumulate, bf16 result; slots with a negative row are skipped. One CTA per token, 16-byte accesses.
+template <int BATCH>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ y,
                    const int* __restrict__ dst_row, const float* __restrict__ w,
@@ -247,18 +258,26 @@ moe_combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
   __syncthreads();
   for (int col = threadIdx.x * 8; col < H; col += blockDim.x * 8) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    // an empty slot (a copy whose experts use fewer than k slots on this rank) adds 0 * 0: no early exit per
-    // slot, so that the loads of four slots are in flight together
-#pragma unroll 4
-    for (int s = 0; s < k; ++s) {
-      const bool live = rows[s] >= 0;
-      const uint4 raw = live ? __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[s] * H + col))
-                             : make_uint4(0u, 0u, 0u, 0u);
-      const float ws = live ? wts[s] : 0.f;
-      acc[0] = fmaf(ws, cab::bf16_lo(raw.x), acc[0]); acc[1] = fmaf(ws, cab::bf16_hi(raw.x), acc[1]);
-      acc[2] = fmaf(ws, cab::bf16_lo(raw.y), acc[2]); acc[3] = fmaf(ws, cab::bf16_hi(raw.y), acc[3]);
-      acc[4] = fmaf(ws, cab::bf16_lo(raw.z), acc[4]); acc[5] = fmaf(ws, cab::bf16_hi(raw.z), acc[5]);
-      acc[6] = fmaf(ws, cab::bf16_lo(raw.w), acc[6]); acc[7] = fmaf(ws, cab::bf16_hi(raw.w), acc[7]);
+    // Slots in batches of BATCH: the batch's row loads are issued together, then added in ascending slot
+    // order; an empty slot (a copy whose experts use fewer than k slots on this rank) contributes 0 * 0.
+    // (BATCH follows k: registers spent on a batch that k cannot fill would only cost resident CTAs.)
+    for (int s0 = 0; s0 < k; s0 += BATCH) {
+      uint4 raw[BATCH];
+      float ws[BATCH];
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int s = s0 + u;
+        const bool live = s < k && rows[s] >= 0;
+        raw[u] = live ? __ldcs(reinterpret_cast<const uint4*>(y + (size_t)rows[s] * H + col)) : make_uint4(0u, 0u, 0u, 0u);
+        ws[u] = live ? wts[s] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        acc[0] = fmaf(ws[u], cab::bf16_lo(raw[u].x), acc[0]); acc[1] = fmaf(ws[u], cab::bf16_hi(raw[u].x), acc[1]);
+        acc[2] = fmaf(ws[u], cab::bf16_lo(raw[u].y), acc[2]); acc[3] = fmaf(ws[u], cab::bf16_hi(raw[u].y), acc[3]);
+        acc[4] = fmaf(ws[u], cab::bf16_lo(raw[u].z), acc[4]); acc[5] = fmaf(ws[u], cab::bf16_hi(raw[u].z), acc[5]);
+        acc[6] = fmaf(ws[u], cab::bf16_lo(raw[u].w), acc[6]); acc[7] = fmaf(ws[u], cab::bf16_hi(raw[u].w), acc[7]);
+      }
     }
     if (extra) {
       const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(extra + (size_t)t * H + col));
@@ -353,6 +372,11 @@ extern "C" int moe_permute_launcher(const int* topk_idx, int T, int k, int E, in
   return cab::launch_status();
 }
 
+static unsigned quant_dispatch_grid(int T, int H) {   // eight warps per CTA, a warp per (token, 1024 columns)
+  const long long warps = (long long)T * ((H + 1023) >> 10);
+  return (unsigned)((warps + 7) / 8);
+}
+
 extern "C" int moe_quant_dispatch_launcher(cab_e4m3* a_q, float* scales_t, const cab_bf16* x,
                                            const int* dst_row, int T, int H, int k, int ld_rows,
                                            int config, cudaStream_t stream) {
@@ -361,7 +385,7 @@ extern "C" int moe_quant_dispatch_launcher(cab_e4m3* a_q, float* scales_t, const
   if (!a_q || !scales_t || !x) return CAB_ERR_BAD_ARGUMENT;
   if (T < 0 || H <= 0 || H % 128 != 0 || k <= 0 || k > 32 || ld_rows <= 0) return CAB_ERR_BAD_ARGUMENT;
   if (!cab::aligned_to(a_q, 16) || !cab::aligned_to(x, 16)) return CAB_ERR_MISALIGNED;
-  moe_quant_dispatch_kernel<false><<<(T + 7) / 8, 256, 0, stream>>>(
+  moe_quant_dispatch_kernel<false><<<quant_dispatch_grid(T, H), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), T, H, k, dst_row, a_q, scales_t, ld_rows);
   return cab::launch_status();
 }
@@ -373,7 +397,7 @@ extern "C" int moe_quant_rows_launcher(cab_e4m3* rows_q, float* scales, const ca
   if (!rows_q || !scales || !x) return CAB_ERR_BAD_ARGUMENT;
   if (T < 0 || H <= 0 || H % 128 != 0 || k <= 0 || k > 32) return CAB_ERR_BAD_ARGUMENT;
   if (!cab::aligned_to(rows_q, 16) || !cab::aligned_to(x, 16)) return CAB_ERR_MISALIGNED;
-  moe_quant_dispatch_kernel<true><<<(T + 7) / 8, 256, 0, stream>>>(
+  moe_quant_dispatch_kernel<true><<<quant_dispatch_grid(T, H), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), T, H, k, dst_row, rows_q, scales, 0);
   return cab::launch_status();
 }
@@ -387,9 +411,13 @@ extern "C" int moe_combine_launcher(cab_bf16* out, const cab_bf16* y, const int*
   if (T < 0 || H <= 0 || H % 8 != 0 || k <= 0 || k > 32) return CAB_ERR_BAD_ARGUMENT;
   if (!cab::aligned_to(out, 16) || !cab::aligned_to(y, 16) || (extra && !cab::aligned_to(extra, 16)))
     return CAB_ERR_MISALIGNED;
-  moe_combine_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(out),
-                                            reinterpret_cast<const __nv_bfloat16*>(y), dst_row, weights,
-                                            reinterpret_cast<const __nv_bfloat16*>(extra), T, H, k);
+  const int threads = cab::row_walk_threads(H / 8);
+  auto* o = reinterpret_cast<__nv_bfloat16*>(out);
+  auto* yy = reinterpret_cast<const __nv_bfloat16*>(y);
+  auto* ex = reinterpret_cast<const __nv_bfloat16*>(extra);
+  if (k <= 2) moe_combine_kernel<2><<<T, threads, 0, stream>>>(o, yy, dst_row, weights, ex, T, H, k);
+  else if (k <= 4) moe_combine_kernel<4><<<T, threads, 0, stream>>>(o, yy, dst_row, weights, ex, T, H, k);
+  else moe_combine_kernel<8><<<T, threads, 0, stream>>>(o, yy, dst_row, weights, ex, T, H, k);
   return cab::launch_status();
 }
 

@@ -512,7 +512,7 @@ class PeerLayer:
                 "by the return kernel (peer memory over NVLink, release/acquire flags, no collective call, no host sync)")
 
     def launches_per_call(self) -> int:
-        return 17 + (3 if self.ops.shared is not None else 0)
+        return 19 + (3 if self.ops.shared is not None else 0)
 
     def close(self) -> None:
         if self.ctx:
