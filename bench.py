@@ -82,6 +82,8 @@ def parse_args():
     ap.add_argument("--min-region-s", type=float, default=MIN_REGION_S)
     ap.add_argument("--ep-tokens", type=int, default=8192,
                     help="moe_ep: tokens per GPU (the benchmark's figure is 8192; smaller values are for profiler captures)")
+    ap.add_argument("--ep-gemm-ctas", type=int, default=0,
+                    help="moe_ep: persistent CTAs of the grouped GEMMs (0 = the launcher's choice)")
     ap.add_argument("--ep-experts", type=int, default=256,
                     help="moe_ep: routed experts over all ranks, a multiple of 8 groups (benchmark: 256)")
     return ap.parse_args()
@@ -401,7 +403,8 @@ def moe_ep_record(ctx: Ctx, cpu_baseline: bool):
     the output (pipelined)."""
     import bench_workloads as bw
     args, torch = ctx.args, ctx.torch
-    wl = bw.MoeEpWorkload(ctx.dev, ctx.rank, ctx.world, T=args.ep_tokens, E=args.ep_experts, mode=args.ep_mode)
+    wl = bw.MoeEpWorkload(ctx.dev, ctx.rank, ctx.world, T=args.ep_tokens, E=args.ep_experts, mode=args.ep_mode,
+                          gemm_ctas=args.ep_gemm_ctas)
     steps, warmup = min(args.steps, 30), min(args.warmup, 5)
     ctx.barrier()                     # every rank's weights and exchange buffers exist before the first call
     out = wl.step()
