@@ -71,11 +71,12 @@ class GdnWorkload:
         self.h2d_bytes = 2 * B * HQ * D * 2 + B * HV * D * 2 + 2 * B * HV * 4
         self.d2h_bytes = B * HV * D * 4
 
-    def step(self, i, config=0):
+    def step(self, i, config=0, zigzag=True):
         j = i % self.N_DISTINCT
-        capi.gdn_decode(self.state, self.out, self.q[j], self.k[j], self.v[j], self.g[j], self.beta[j], config)
+        cfg = capi.gdn_loop_config(i, config) if zigzag else config
+        capi.gdn_decode(self.state, self.out, self.q[j], self.k[j], self.v[j], self.g[j], self.beta[j], cfg)
 
-    def make_e2e(self, config=0):
+    def make_e2e(self, config=0, zigzag=True):
         """End-to-end step through cuda_extension.gdn_decode_forward. A step's q/k/v/g/beta sit in ONE pinned
         staging record and reach the GPU with one copy; the output goes back with one copy; uploads, compute
         and downloads of neighbouring steps overlap on three streams (two slots)."""
@@ -103,7 +104,7 @@ class GdnWorkload:
             slots[s].copy_(host[i % n], non_blocking=True)
 
         def compute(i, s):
-            o, _ = ext.gdn_decode_forward(state, *slot_views[s], config)
+            o, _ = ext.gdn_decode_forward(state, *slot_views[s], capi.gdn_loop_config(i, config) if zigzag else config)
             return o
 
         def download(o, s):

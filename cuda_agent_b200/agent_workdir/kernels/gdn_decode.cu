@@ -117,8 +117,12 @@ template <int PAIRS>
 __global__ void __launch_bounds__(kWarpsPerCta * cab::kWarp)
 gdn_decode_v8_kernel(float* __restrict__ state, float* __restrict__ out, const uint4* __restrict__ q,
                      const uint4* __restrict__ k, const __nv_bfloat16* __restrict__ v,
-                     const float* __restrict__ g, const float* __restrict__ beta, int Hq, int Hv, int group) {
-  const int unit = blockIdx.x;
+                     const float* __restrict__ g, const float* __restrict__ beta, int Hq, int Hv, int group,
+                     int reverse) {
+  // CTAs start roughly in blockIdx order; `reverse` walks the (b, hv) units from the last to the first. A decode
+  // loop that alternates the direction starts every step with the units the previous step wrote last, of which
+  // about 80 MB are still in L2 (measured: 946 MB of DRAM traffic per step instead of 1081 MB).
+  const int unit = reverse ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
   const int b = unit / Hv;
   const int hv = unit - b * Hv;
   const int qk_unit = b * Hq + hv / group;
@@ -202,8 +206,13 @@ extern "C" int gdn_decode_launcher(float* state, float* out, const cab_bf16* q, 
   if (!cab::aligned_to(state, 16) || !cab::aligned_to(out, 16) || !cab::aligned_to(q, 8) ||
       !cab::aligned_to(k, 8) || !cab::aligned_to(v, 2))
     return CAB_ERR_MISALIGNED;
-  // config 0 (default) and 3 use 256-bit accesses (half-warp per row); they need a 32-byte aligned state
-  // and 16-byte aligned q/k, otherwise the 128-bit kernel with the same amount in flight takes over.
+  // config bit 4 (16): walk the (b, hv) units from the last to the first (256-bit kernels). A caller that flips
+  // it from step to step of a decode loop starts every step on the rows the previous step wrote last, which
+  // are still in L2; a single step computes the same thing either way. The low four bits choose the kernel
+  // form: 0 (default) and 3 use 256-bit accesses (half-warp per row); they need a 32-byte aligned state and
+  // 16-byte aligned q/k, otherwise the 128-bit kernel with the same amount in flight takes over.
+  const int reverse = (config >= 0 && (config & 16)) ? 1 : 0;
+  if (config >= 0) config &= 15;
   const bool v8_ok = cab::aligned_to(state, 32) && cab::aligned_to(q, 16) && cab::aligned_to(k, 16);
   if ((config == 3 || config < 1 || config > 4) && v8_ok) {
     const unsigned grid = static_cast<unsigned>(B) * static_cast<unsigned>(Hv);
@@ -211,9 +220,9 @@ extern "C" int gdn_decode_launcher(float* state, float* out, const cab_bf16* q, 
     const uint4* k4 = reinterpret_cast<const uint4*>(k);
     const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(v);
     if (config == 3)
-      gdn_decode_v8_kernel<4><<<grid, kWarpsPerCta * cab::kWarp, 0, stream>>>(state, out, q4, k4, vb, g, beta, Hq, Hv, Hv / Hq);
+      gdn_decode_v8_kernel<4><<<grid, kWarpsPerCta * cab::kWarp, 0, stream>>>(state, out, q4, k4, vb, g, beta, Hq, Hv, Hv / Hq, reverse);
     else
-      gdn_decode_v8_kernel<8><<<grid, kWarpsPerCta * cab::kWarp, 0, stream>>>(state, out, q4, k4, vb, g, beta, Hq, Hv, Hv / Hq);
+      gdn_decode_v8_kernel<8><<<grid, kWarpsPerCta * cab::kWarp, 0, stream>>>(state, out, q4, k4, vb, g, beta, Hq, Hv, Hv / Hq, reverse);
     return cab::launch_status();
   }
   switch (config) {

@@ -120,6 +120,16 @@ def axpby(out, a, b, alpha: float, config: int = 0) -> None:
            lib().axpby_launcher(_p(out), _p(a), _p(b), alpha, a.numel(), config, _stream()))
 
 
+GDN_REVERSE = 16
+
+
+def gdn_loop_config(step: int, config: int = 0) -> int:
+    """`config` for step `step` of a decode loop on one state: the reverse-walk bit on odd steps, so that every
+    step starts on the rows the previous one wrote last (still in L2). The result of a step does not depend on
+    the bit."""
+    return (config & 15) | (GDN_REVERSE if step & 1 else 0)
+
+
 def gdn_decode(state, out, q, k, v, g, beta, config: int = 0) -> None:
     """One decode step; `state` [B,Hv,128,128] fp32 is updated in place, `out` [B,Hv,128] fp32."""
     B, Hv = state.shape[0], state.shape[1]

@@ -21,7 +21,7 @@ class GdnDecodeGraph:
     them between replays.
     """
 
-    def __init__(self, state, out, q, k, v, g, beta, config: int = 0):
+    def __init__(self, state, out, q, k, v, g, beta, config: int = 0, zigzag: bool = True):
         self.tensors = (state, out, q, k, v, g, beta)
         steps = q.shape[0]
         per_step_out = out.dim() == 4
@@ -33,7 +33,9 @@ class GdnDecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             for s in range(steps):
-                capi.gdn_decode(state, out[s] if per_step_out else out, q[s], k[s], v[s], g[s], beta[s], config)
+                # zig-zag: odd steps walk the state backwards, so each starts on what its predecessor left in L2
+                cfg = capi.gdn_loop_config(s, config) if zigzag else config
+                capi.gdn_decode(state, out[s] if per_step_out else out, q[s], k[s], v[s], g[s], beta[s], cfg)
         self.steps = steps
 
     def replay(self) -> None:

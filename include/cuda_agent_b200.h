@@ -91,6 +91,11 @@ int axpby_launcher(float* out, const float* a, const float* b, float alpha, int 
 /* warp per row, 4 / 8 / 16 rows in flight. Configs 1, 2, 4 give identical bits;  */
 /* 0 and 3 reduce the dot products in a different order and agree with them to    */
 /* fp32 rounding. One launch reads and writes each state element exactly once.   */
+/* The low four bits of config are that choice. Bit 4 (16), with configs 0 / 3:   */
+/* walk the (b, hv) units from the last to the first. A decode loop that flips it  */
+/* from step to step (0, 16, 0, ...) starts every step on the rows the previous    */
+/* one wrote last, of which about 80 MB are still in L2. The result of a step does */
+/* not depend on the bit.                                                          */
 /* ------------------------------------------------------------------------- */
 int gdn_decode_launcher(float* state, float* out, const cab_bf16* q, const cab_bf16* k,
                         const cab_bf16* v, const float* g, const float* beta, int B, int Hq,

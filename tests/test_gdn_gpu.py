@@ -31,7 +31,7 @@ def run_capi(dev, S, q, k, v, g, beta, config=0):
     return out, Sd
 
 
-@pytest.mark.parametrize("config", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("config", [0, 1, 2, 3, 4, 16, 19, 17])   # 16: the units walked from last to first
 @pytest.mark.parametrize("B,Hq,Hv", [(4, 8, 8), (1, 1, 1), (3, 2, 4), (5, 1, 6), (2, 16, 32)])
 def test_matches_oracle(cuda_device, B, Hq, Hv, config):
     m = load_oracle("gdn", {"CAB_GDN_CONFIG": 0})
@@ -65,6 +65,10 @@ def test_launch_variants_agree(cuda_device):
     wide = [run_capi(cuda_device, S, *step, config=c) for c in (0, 3)]            # 256-bit variants
     assert torch.equal(wide[0][0], wide[1][0]) and torch.equal(wide[0][1], wide[1][1])
     torch.testing.assert_close(wide[0][1], results[0][1], rtol=1e-5, atol=1e-7)
+    # the direction of the walk changes nothing in the result
+    for c in (16, 19):
+        o, S_new = run_capi(cuda_device, S, *step, config=c)
+        assert torch.equal(o, wide[0][0]) and torch.equal(S_new, wide[0][1]), c
     # an unaligned state falls back to the 128-bit kernel
     from cuda_agent_b200 import capi
     pad = torch.zeros(S.numel() + 4, device=cuda_device)
@@ -91,6 +95,29 @@ def test_multi_step_recurrence_stays_within_tolerance(cuda_device):
         capi.gdn_decode(Sd, out, *[t.to(cuda_device) for t in step])
         assert_rel(out, o_ref, what="o")
     assert_rel(Sd, S_ref, what="state after 16 steps")
+
+
+def test_full_size_zigzag_loop_equals_forward_loop(cuda_device):
+    """Eight chained full-size steps (512 MiB of state) with the direction of the walk alternating, against the
+    same eight steps walked forwards: bit-identical state and outputs."""
+    from cuda_agent_b200 import capi
+    m = load_oracle("gdn", {"CAB_GDN_CONFIG": 1})
+    B, Hq, Hv = m.get_init_inputs()
+    dev = cuda_device
+    gd = torch.Generator(device=dev).manual_seed(77)
+    S0 = torch.randn(B, Hv, 128, 128, device=dev, generator=gd) * 0.02
+    gen = torch.Generator().manual_seed(78)
+    steps = [[t.to(dev) for t in m.make_step_inputs(B, Hq, Hv, gen)] for _ in range(8)]
+    outs = []
+    for zigzag in (False, True):
+        S = S0.clone()
+        o = torch.empty(8, B, Hv, 128, device=dev)
+        for i, step in enumerate(steps):
+            capi.gdn_decode(S, o[i], *step, capi.gdn_loop_config(i) if zigzag else 0)
+        torch.cuda.synchronize()
+        outs.append((S, o))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert [capi.gdn_loop_config(i, 3) for i in range(3)] == [3, 19, 3]
 
 
 def test_full_size_properties(cuda_device):
