@@ -424,6 +424,26 @@ class PeerLayer:
         # entries this rank can receive per call: everything when alone, else 1.5 x the balanced share
         self.entry_cap = entry_cap or (t_cap * ops.k if world == 1 else (t_cap * ops.k * 3) // 2)
         self.ctx = ctypes.c_void_p()
+        local_error = None
+        try:
+            self._create_local(ops, rank, world, t_cap)
+        except Exception as exc:  # noqa: BLE001  (reported below, on every rank)
+            local_error = exc
+        if _connect and world > 1:
+            # a rank that could not build its side still answers here, so that the others do not wait for it
+            errors = [None] * world
+            dist.all_gather_object(errors, None if local_error is None else repr(local_error), group=group)
+            bad = {r: e for r, e in enumerate(errors) if e is not None}
+            if bad:
+                raise RuntimeError(f"expert-parallel layer could not be built on rank(s) {bad}")
+        elif local_error is not None:
+            raise local_error
+        if _connect:
+            self._connect_ipc(group)
+
+    def _create_local(self, ops, rank, world, t_cap):
+        import ctypes
+        capi = self.capi
         with torch.cuda.device(ops.dev):
             capi._check("moe_ep_peer_create",
                         self.lib.moe_ep_peer_create(ctypes.byref(self.ctx), rank, world, t_cap, ops.H, ops.k,
@@ -437,22 +457,34 @@ class PeerLayer:
         if nbytes == 0:
             raise ValueError("moe_ep_peer_workspace_bytes rejected the layer's shapes")
         self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=ops.dev)
-        if _connect:
-            self._connect_ipc(group)
 
     def _connect_ipc(self, group):
+        """Swap the buffers' IPC handles and map the peers'. A rank whose export or mapping fails still takes
+        part in both exchanges and every rank raises, so that no rank is left waiting in a collective."""
         import ctypes
         mine = (ctypes.c_ubyte * 64)()
         with torch.cuda.device(self.ops.dev):
-            self.capi._check("moe_ep_peer_export", self.lib.moe_ep_peer_export(self.ctx, mine))
+            rc = self.lib.moe_ep_peer_export(self.ctx, mine)
         if self.world == 1:
+            self.capi._check("moe_ep_peer_export", rc)
             handles = bytes(mine)
         else:
             gathered = [None] * self.world
-            dist.all_gather_object(gathered, bytes(mine), group=group)
-            handles = b"".join(gathered)
+            dist.all_gather_object(gathered, (rc, bytes(mine)), group=group)
+            bad = [r for r, (code, _) in enumerate(gathered) if code != 0]
+            if bad:
+                raise RuntimeError(f"moe_ep_peer_export failed on rank(s) {bad}")
+            handles = b"".join(h for _, h in gathered)
         with torch.cuda.device(self.ops.dev):
-            self.capi._check("moe_ep_peer_connect_ipc", self.lib.moe_ep_peer_connect_ipc(self.ctx, handles))
+            rc = self.lib.moe_ep_peer_connect_ipc(self.ctx, handles)
+        if self.world > 1:
+            codes = [None] * self.world
+            dist.all_gather_object(codes, rc, group=group)
+            bad = [r for r, code in enumerate(codes) if code != 0]
+            if bad:
+                raise RuntimeError(f"moe_ep_peer_connect_ipc failed on rank(s) {bad}")
+        else:
+            self.capi._check("moe_ep_peer_connect_ipc", rc)
 
     @staticmethod
     def build_local(ops_per_rank, t_cap: int, entry_cap=None):
