@@ -7,7 +7,9 @@ One JSON line on rank 0. Headline workload ("gdn_decode_serving"): B=256 sequenc
 shared by groups of 2 across 32 value heads, dk=dv=128, fp32 state of 512 MiB per GPU. One step is one decode
 step (one kernel launch over the whole batch) with that step's own q/k/v/g/beta, taken in turn from 64
 pre-generated seeded steps. Algorithmic bytes per step per GPU: state read + write 2*536870912, q and k
-2*1048576, v 2097152, g and beta 2*32768, o 4194304 = 1082195968.
+2*1048576, v 2097152, g and beta 2*32768, o 4194304 = 1082195968. Consecutive steps walk the state in alternating
+directions (--gdn-walk zigzag, the default: the op's config bit 4 on odd steps), so a step starts on the rows the
+previous one wrote last and finds about 80 MB of them in L2; --gdn-walk forward walks every step the same way.
 
 Keys of the line:
   value        GB/s over all GPUs with every input already in HBM (CUDA events, max over ranks)
