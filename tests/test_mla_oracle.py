@@ -34,6 +34,17 @@ def test_matches_float64_restatement():
     assert np.abs(out.double().numpy() - ref).max() < 0.01 * np.abs(ref).max() + 4e-3   # bf16 rounding only
 
 
+def test_matches_float64_restatement_at_the_benchmark_shape():
+    """Two sequences of the benchmark's shape (128 heads, 2048 of up to 32768 cached rows) against the float64 loop."""
+    m = load_oracle("mla", {"CAB_MLA_CONFIG": 2})
+    q, kv, seq_len, idx = m.make_inputs(2, 128, 32768, 2048, 8192, torch.Generator().manual_seed(31))
+    idx[1, 0, 100:140] = -1
+    out = m.Model(*m.get_init_inputs())(q, kv, seq_len, idx)
+    ref = mla_f64(q, kv, seq_len, idx)
+    assert out.shape == (2, 1, 128, 512)
+    assert np.abs(out.double().numpy() - ref).max() < 0.01 * np.abs(ref).max() + 4e-3   # bf16 rounding only
+
+
 def test_hand_cases():
     m = load_oracle("mla", {"CAB_MLA_CONFIG": 0})
     kv = torch.zeros(1, 8, 576, dtype=torch.bfloat16)

@@ -173,6 +173,20 @@ def test_layer_matches_float64_restatement(cfg):
     assert np.isfinite(out).all() and np.abs(out).max() > 0
 
 
+def test_layer_matches_float64_restatement_at_benchmark_width():
+    """The same check with the benchmark layer's H 2048 / I 1024 (16 and 8 scale blocks per row) and top-6 of
+    8 experts: the float64 restatement is independent of the oracle's blocked fp32 arithmetic."""
+    m = load_oracle("moe", {"CAB_MOE_CONFIG": 0})
+    torch.manual_seed(99)
+    model = m.Model(12, 2048, 1024, 8, 6, "softmax", 1, 1, False)
+    x = torch.randn(12, 2048, generator=torch.Generator().manual_seed(98)).to(torch.bfloat16)
+    out = model(x).double().numpy()
+    ref = layer_f64(model, x)
+    rel = np.linalg.norm(out - ref) / np.linalg.norm(ref)
+    assert rel < 6e-3, rel
+    assert np.isfinite(out).all() and np.abs(out).max() > 0
+
+
 def test_state_dict_names():
     m = load_oracle("moe", {"CAB_MOE_CONFIG": 1})
     model = m.Model(*m.get_init_inputs())
