@@ -263,6 +263,8 @@ def gdn_record(ctx: Ctx, cpu_baseline: bool):
     zz = args.gdn_walk == "zigzag"
     ms, n = ctx.timed(lambda i: wl.step(i, args.config, zz), args.steps, args.warmup)
     assert bool(torch.isfinite(wl.out).all()), "non-finite decode output"
+    # the other walk, for the record: with every step walked forwards nothing of the state is found in L2
+    other_ms, _ = ctx.timed(lambda i: wl.step(i, args.config, not zz), args.steps, 3)
     graph = None
     if args.graph:
         from cuda_agent_b200.graphs import GdnDecodeGraph
@@ -290,6 +292,12 @@ def gdn_record(ctx: Ctx, cpu_baseline: bool):
                 "h2d_bytes_per_step": wl.h2d_bytes * world, "d2h_bytes_per_step": wl.d2h_bytes * world,
                 "ms_per_step": round(e2e_ms, 5), "steps": e2e_n, "api": "cuda_extension.gdn_decode_forward",
                 "copies_per_step": "1 host->device (packed q,k,v,g,beta), 1 device->host"},
+        "walk": {"timed": args.gdn_walk, "other": "forward" if zz else "zigzag",
+                 "other_value": round(wl.bytes_per_step * world / (other_ms * 1e-3) / 1e9, 2),
+                 "other_ms_per_step": round(other_ms, 5),
+                 "note": "zigzag: consecutive steps walk the state in alternating directions and find about 80 MB "
+                         "of it in L2; forward: every step walks it the same way (what a model with many such "
+                         "layers would see)"},
         "gpu_launches": n,
         "roofline": {"bound": "hbm", "kernel": kernel, "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(per_gpu / peak, 4), "traffic": NCU_TRAFFIC[kernel if zz else kernel + " forward"],
